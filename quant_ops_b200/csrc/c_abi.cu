@@ -1,0 +1,380 @@
+// extern "C" entry points: argument validation, kernel selection, workspaces.  No kernels live here.
+#include <cstring>
+#include <mutex>
+
+#include "qo_internal.cuh"
+
+namespace qo {
+
+static thread_local char t_error[512] = "";
+static thread_local int t_policy = 0;
+static thread_local int t_quant_path = 0;
+static thread_local int t_gemm_path = 0;
+std::atomic<uint64_t> g_launches{0};
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(t_error, sizeof t_error, fmt, ap);
+  va_end(ap);
+}
+void clear_error() { t_error[0] = 0; }
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+
+// The kernels are built for sm_100a only; anything else cannot run them.
+int require_device(int* dev_out) {
+  static std::atomic<int> ok[kMaxDevices];  // 0 unknown, 1 good, 2 bad
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(QO_ERR_NO_DEVICE, "no CUDA device available: %s", cudaGetErrorString(e));
+  }
+  if (dev_out) *dev_out = dev;
+  if (dev < 0 || dev >= kMaxDevices) return fail(QO_ERR_NO_DEVICE, "device index %d out of range", dev);
+  int state = ok[dev].load(std::memory_order_relaxed);
+  if (state == 0) {
+    int major = 0;
+    QO_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    state = (major == 10) ? 1 : 2;
+    ok[dev].store(state, std::memory_order_relaxed);
+  }
+  if (state != 1) return fail(QO_ERR_NO_DEVICE, "device %d is not an sm_100 GPU; this library has sm_100a kernels only", dev);
+  return QO_OK;
+}
+
+// Grow-only per-device scratch the library owns when the caller passes no workspace.
+struct Scratch {
+  std::mutex mu;
+  void* ptr[kMaxDevices] = {};
+  size_t bytes[kMaxDevices] = {};
+};
+Scratch g_scratch;       // GEMM / fused layer
+Scratch g_host_staging;  // device side of the host-buffer quantizer
+
+int scratch_get(Scratch& s, int dev, size_t need, void** out) {
+  std::lock_guard<std::mutex> lock(s.mu);
+  if (s.bytes[dev] < need) {
+    if (s.ptr[dev]) {
+      QO_CUDA_TRY(cudaDeviceSynchronize());
+      QO_CUDA_TRY(cudaFree(s.ptr[dev]));
+      s.ptr[dev] = nullptr;
+      s.bytes[dev] = 0;
+    }
+    size_t grow = need + need / 4;
+    QO_CUDA_TRY(cudaMalloc(&s.ptr[dev], grow));
+    s.bytes[dev] = grow;
+  }
+  *out = s.ptr[dev];
+  return QO_OK;
+}
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+int check_quant_args(const void* x, int64_t ldx, const void* left, const void* right, const void* codes,
+                     const void* scales, int64_t tokens, int m, int n, int in_dtype, int pack, int scale_dtype) {
+  if (tokens < 0) return fail(QO_ERR_INVALID_ARGUMENT, "flatquant: tokens = %lld is negative", (long long)tokens);
+  if (m <= 0 || n <= 0) return fail(QO_ERR_INVALID_ARGUMENT, "flatquant: transform sizes must be positive (m=%d n=%d)", m, n);
+  if (!dtype_ok(in_dtype)) return fail(QO_ERR_INVALID_ARGUMENT, "flatquant: unknown in_dtype %d", in_dtype);
+  if (!dtype_ok(scale_dtype)) return fail(QO_ERR_INVALID_ARGUMENT, "flatquant: unknown scale_dtype %d", scale_dtype);
+  const int64_t feat = (int64_t)m * n;
+  if (feat > (1 << 20)) return fail(QO_ERR_INVALID_ARGUMENT, "flatquant: m*n = %lld is not a plausible feature count", (long long)feat);
+  if (ldx < feat) return fail(QO_ERR_INVALID_ARGUMENT, "flatquant: row stride %lld is smaller than m*n = %lld", (long long)ldx, (long long)feat);
+  if (pack && feat % 8) return fail(QO_ERR_INVALID_ARGUMENT, "flatquant: features (%lld) must be divisible by 8 for int32 packing", (long long)feat);
+  if (tokens > 0 && (!x || !left || !right || !codes || !scales)) return fail(QO_ERR_INVALID_ARGUMENT, "flatquant: null pointer argument");
+  return QO_OK;
+}
+
+}  // namespace
+}  // namespace qo
+
+using namespace qo;
+
+extern "C" {
+
+int qo_version(void) { return 100; }
+
+const char* qo_status_string(int status) {
+  switch (status) {
+    case QO_OK: return "ok";
+    case QO_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case QO_ERR_UNSUPPORTED: return "unsupported";
+    case QO_ERR_CUDA: return "CUDA error";
+    case QO_ERR_NO_DEVICE: return "no sm_100 device";
+    case QO_ERR_WORKSPACE: return "workspace too small";
+    case QO_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";
+  }
+  return "unknown status";
+}
+
+const char* qo_last_error(void) { return t_error; }
+
+uint64_t qo_kernel_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+int qo_last_quantizer_path(void) { return t_quant_path; }
+int qo_last_gemm_path(void) { return t_gemm_path; }
+
+int qo_set_kernel_policy(int policy) {
+  if (policy < 0 || policy > 2) return fail(QO_ERR_INVALID_ARGUMENT, "kernel policy must be 0, 1 or 2");
+  t_policy = policy;
+  return QO_OK;
+}
+
+int qo_get_decompose_dim(int64_t n, int64_t* m_out, int64_t* n_out) {
+  if (!m_out || !n_out) return fail(QO_ERR_INVALID_ARGUMENT, "get_decompose_dim: null output pointer");
+  if (n <= 0) return fail(QO_ERR_INVALID_ARGUMENT, "get_decompose_dim: n must be positive");
+  if (n % 4 == 2) return fail(QO_ERR_INVALID_ARGUMENT, "get_decompose_dim: %lld = 2 (mod 4) is not a difference of two squares", (long long)n);
+  auto isqrt = [](int64_t v) {
+    int64_t r = (int64_t)__builtin_sqrtl((long double)v);
+    while (r * r > v) --r;
+    while ((r + 1) * (r + 1) <= v) ++r;
+    return r;
+  };
+  int64_t a = isqrt(n);
+  if (a * a < n) ++a;
+  for (;; ++a) {
+    const int64_t d = a * a - n, b = isqrt(d);
+    if (b * b == d) {
+      *m_out = a - b;
+      *n_out = a + b;
+      return QO_OK;
+    }
+  }
+}
+
+int qo_flatquant_quantize(const void* x, int64_t ldx, const void* left, const void* right, void* codes, void* scales,
+                          int64_t tokens, int m, int n, float clip_ratio, int in_dtype, int pack_int32,
+                          int scale_dtype, void* stream) {
+  clear_error();
+  int rc = check_quant_args(x, ldx, left, right, codes, scales, tokens, m, n, in_dtype, pack_int32, scale_dtype);
+  if (rc) return rc;
+  if (tokens == 0) return QO_OK;
+  if ((rc = require_device(nullptr))) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const bool fast_ok = flatquant_sm100_supported(ldx, m, n, in_dtype, x);
+  if (t_policy == 2 && !fast_ok)
+    return fail(QO_ERR_UNSUPPORTED, "flatquant: no tcgen05 kernel for m=%d n=%d dtype=%d ldx=%lld", m, n, in_dtype, (long long)ldx);
+  if (fast_ok && t_policy != 1) {
+    t_quant_path = 2;
+    return launch_flatquant_sm100(x, ldx, left, right, codes, scales, tokens, m, n, clip_ratio, in_dtype, pack_int32,
+                                  scale_dtype, st);
+  }
+  t_quant_path = 1;
+  return launch_flatquant_generic(x, ldx, left, right, codes, scales, tokens, m, n, clip_ratio, in_dtype, pack_int32,
+                                  scale_dtype, st);
+}
+
+int qo_dequantize_int4(const void* codes, const void* scales, float* out, int64_t tokens, int64_t features,
+                       int packed_int32, int scale_dtype, void* stream) {
+  clear_error();
+  if (tokens < 0 || features < 0) return fail(QO_ERR_INVALID_ARGUMENT, "dequantize: negative size");
+  if (!dtype_ok(scale_dtype)) return fail(QO_ERR_INVALID_ARGUMENT, "dequantize: unknown scale_dtype %d", scale_dtype);
+  if (packed_int32 && features % 8) return fail(QO_ERR_INVALID_ARGUMENT, "dequantize: packed input needs features %% 8 == 0");
+  if (tokens == 0 || features == 0) return QO_OK;
+  if (!codes || !scales || !out) return fail(QO_ERR_INVALID_ARGUMENT, "dequantize: null pointer argument");
+  if (reinterpret_cast<uintptr_t>(out) % 16) return fail(QO_ERR_INVALID_ARGUMENT, "dequantize: out must be 16-byte aligned");
+  int rc = require_device(nullptr);
+  if (rc) return rc;
+  return launch_dequantize(codes, scales, out, tokens, features, packed_int32, scale_dtype,
+                           reinterpret_cast<cudaStream_t>(stream));
+}
+
+size_t qo_int4_matmul_workspace_bytes(int64_t tokens, int64_t k, int64_t n_out) {
+  return gemm_sm100_workspace_bytes(tokens, k, n_out);
+}
+
+static int int4_matmul_impl(const int32_t* a, int64_t lda, const int32_t* b, int64_t bsk, int64_t bsn,
+                            const float* sa, const float* sb, void* out, int out_dtype, int64_t t, int64_t k,
+                            int64_t n, int32_t* acc_out, const void* bias, void* workspace, size_t workspace_bytes,
+                            cudaStream_t st) {
+  if (t < 0 || k < 0 || n < 0) return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: negative size");
+  if (k % 8) return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: k = %lld must be a multiple of 8", (long long)k);
+  if (k > 262143) return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: k = %lld is beyond the supported reduction length", (long long)k);
+  if (out_dtype != QO_F16 && out_dtype != QO_BF16) return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: out_dtype must be QO_F16 or QO_BF16");
+  if (t == 0 || n == 0) return QO_OK;
+  if (!a || !b || !sa || !sb || !out) return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: null pointer argument");
+  if (lda < k / 8) return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: lda smaller than k/8");
+  int dev = 0, rc = require_device(&dev);
+  if (rc) return rc;
+  const bool fast_ok = k > 0 && gemm_sm100_supported(t, k, n, lda, bsk, bsn);
+  if (t_policy == 2 && !fast_ok)
+    return fail(QO_ERR_UNSUPPORTED, "int4_matmul: no tcgen05 kernel for t=%lld k=%lld n=%lld", (long long)t, (long long)k, (long long)n);
+  if (fast_ok && t_policy != 1) {
+    const size_t need = gemm_sm100_workspace_bytes(t, k, n);
+    if (workspace == nullptr && need > 0) {
+      if ((rc = scratch_get(g_scratch, dev, need, &workspace))) return rc;
+      workspace_bytes = need;
+    }
+    if (workspace_bytes < need) return fail(QO_ERR_WORKSPACE, "int4_matmul: workspace of %zu bytes, need %zu", workspace_bytes, need);
+    t_gemm_path = 2;
+    return launch_gemm_sm100(a, lda, b, bsk, bsn, sa, sb, out, out_dtype, t, k, n, acc_out, bias, workspace,
+                             workspace_bytes, st);
+  }
+  t_gemm_path = 1;
+  return launch_gemm_generic(a, lda, b, bsk, bsn, sa, sb, out, out_dtype, t, k, n, acc_out, bias, st);
+}
+
+int qo_int4_matmul(const int32_t* a, int64_t lda, const int32_t* b, int64_t b_stride_k, int64_t b_stride_n,
+                   const float* scale_a, const float* scale_b, void* out, int out_dtype, int64_t tokens, int64_t k,
+                   int64_t n_out, int32_t* acc_out, void* workspace, size_t workspace_bytes, void* stream) {
+  clear_error();
+  return int4_matmul_impl(a, lda, b, b_stride_k, b_stride_n, scale_a, scale_b, out, out_dtype, tokens, k, n_out,
+                          acc_out, nullptr, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
+}
+
+size_t qo_w4a4_linear_workspace_bytes(int64_t tokens, int64_t k, int64_t n_out) {
+  if (tokens <= 0 || k <= 0) return 0;
+  return align_up((size_t)tokens * (size_t)(k / 8) * 4, 256) + align_up((size_t)tokens * 4, 256) +
+         gemm_sm100_workspace_bytes(tokens, k, n_out);
+}
+
+int qo_w4a4_linear(const void* x, int64_t ldx, const void* left, const void* right, const int32_t* w_packed,
+                   const float* w_scale, const void* bias, void* out, int64_t tokens, int m, int n, int64_t n_out,
+                   float clip_ratio, int in_dtype, int out_dtype, void* workspace, size_t workspace_bytes,
+                   void* stream) {
+  clear_error();
+  if (n_out < 0) return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear: negative n_out");
+  const int64_t k = (int64_t)m * n;
+  if (m <= 0 || n <= 0 || k % 8) return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear: m*n must be a positive multiple of 8");
+  if (tokens == 0 || n_out == 0) return QO_OK;
+  if (!w_packed || !w_scale || !out) return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear: null pointer argument");
+  int dev = 0, rc = require_device(&dev);
+  if (rc) return rc;
+  const size_t need = qo_w4a4_linear_workspace_bytes(tokens, k, n_out);
+  if (workspace == nullptr) {
+    if ((rc = scratch_get(g_scratch, dev, need, &workspace))) return rc;
+    workspace_bytes = need;
+  }
+  if (workspace_bytes < need) return fail(QO_ERR_WORKSPACE, "w4a4_linear: workspace of %zu bytes, need %zu", workspace_bytes, need);
+  char* ws = reinterpret_cast<char*>(workspace);
+  int32_t* a_packed = reinterpret_cast<int32_t*>(ws);
+  const size_t off_scale = align_up((size_t)tokens * (size_t)(k / 8) * 4, 256);
+  float* a_scale = reinterpret_cast<float*>(ws + off_scale);
+  const size_t off_gemm = off_scale + align_up((size_t)tokens * 4, 256);
+  rc = qo_flatquant_quantize(x, ldx, left, right, a_packed, a_scale, tokens, m, n, clip_ratio, in_dtype, 1, QO_F32, stream);
+  if (rc) return rc;
+  // weights are [n_out, k/8] with K contiguous: as the GEMM's B operand that is strides (1, k/8)
+  return int4_matmul_impl(a_packed, k / 8, w_packed, 1, k / 8, a_scale, w_scale, out, out_dtype, tokens, k, n_out,
+                          nullptr, bias, ws + off_gemm, workspace_bytes - off_gemm,
+                          reinterpret_cast<cudaStream_t>(stream));
+}
+
+int qo_pack_int4(const int8_t* codes, int32_t* packed, int64_t rows, int64_t features, void* stream) {
+  clear_error();
+  if (rows < 0 || features < 0 || features % 8) return fail(QO_ERR_INVALID_ARGUMENT, "pack_int4: features (%lld) must be divisible by 8", (long long)features);
+  if (rows == 0 || features == 0) return QO_OK;
+  if (!codes || !packed) return fail(QO_ERR_INVALID_ARGUMENT, "pack_int4: null pointer argument");
+  if (reinterpret_cast<uintptr_t>(codes) % 8) return fail(QO_ERR_INVALID_ARGUMENT, "pack_int4: codes must be 8-byte aligned");
+  int rc = require_device(nullptr);
+  if (rc) return rc;
+  return launch_pack(codes, packed, rows, features, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int qo_unpack_int4(const int32_t* packed, int8_t* codes, int64_t rows, int64_t features, void* stream) {
+  clear_error();
+  if (rows < 0 || features < 0 || features % 8) return fail(QO_ERR_INVALID_ARGUMENT, "unpack_int4: features (%lld) must be divisible by 8", (long long)features);
+  if (rows == 0 || features == 0) return QO_OK;
+  if (!codes || !packed) return fail(QO_ERR_INVALID_ARGUMENT, "unpack_int4: null pointer argument");
+  if (reinterpret_cast<uintptr_t>(codes) % 8) return fail(QO_ERR_INVALID_ARGUMENT, "unpack_int4: codes must be 8-byte aligned");
+  int rc = require_device(nullptr);
+  if (rc) return rc;
+  return launch_unpack(packed, codes, rows, features, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int qo_quantize_weights_int4(const float* w, int32_t* packed, float* scale, int64_t rows, int64_t k, void* stream) {
+  clear_error();
+  if (rows < 0 || k < 0 || k % 8) return fail(QO_ERR_INVALID_ARGUMENT, "quantize_weights: k (%lld) must be divisible by 8", (long long)k);
+  if (rows == 0 || k == 0) return QO_OK;
+  if (!w || !packed || !scale) return fail(QO_ERR_INVALID_ARGUMENT, "quantize_weights: null pointer argument");
+  int rc = require_device(nullptr);
+  if (rc) return rc;
+  return launch_quantize_weights(w, packed, scale, rows, k, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// Host-buffer quantizer: rows go through a ring of device slots, one stream per slot, so the copy in of slice
+// i+1, the kernel on slice i and the copy out of slice i-1 overlap.
+int qo_flatquant_quantize_host(const void* x_host, const void* left_host, const void* right_host, void* codes_host,
+                               void* scales_host, int64_t tokens, int m, int n, float clip_ratio, int in_dtype,
+                               int pack_int32, int scale_dtype) {
+  clear_error();
+  int rc = check_quant_args(x_host, (int64_t)m * n, left_host, right_host, codes_host, scales_host, tokens, m, n,
+                            in_dtype, pack_int32, scale_dtype);
+  if (rc) return rc;
+  if (tokens == 0) return QO_OK;
+  int dev = 0;
+  if ((rc = require_device(&dev))) return rc;
+
+  constexpr int kSlots = 4;
+  static std::mutex mu;
+  static cudaStream_t streams[kMaxDevices][kSlots] = {};
+  std::lock_guard<std::mutex> lock(mu);  // one host-buffer call at a time per process: the slots are shared
+  for (int s = 0; s < kSlots; ++s)
+    if (!streams[dev][s]) QO_CUDA_TRY(cudaStreamCreateWithFlags(&streams[dev][s], cudaStreamNonBlocking));
+
+  const size_t feat = (size_t)m * n, esz = dtype_size(in_dtype), ssz = dtype_size(scale_dtype);
+  const size_t code_row = pack_int32 ? feat / 2 : feat;
+  int64_t slice = (int64_t)((24u << 20) / (feat * esz));  // about 24 MB of activations per slice
+  if (slice < 1) slice = 1;
+  if (slice > tokens) slice = tokens;
+  const size_t x_bytes = align_up((size_t)slice * feat * esz, 256), c_bytes = align_up((size_t)slice * code_row, 256),
+               s_bytes = align_up((size_t)slice * ssz, 256), lr_bytes = align_up(((size_t)m * m + (size_t)n * n) * esz, 256);
+  void* base = nullptr;
+  if ((rc = scratch_get(g_host_staging, dev, lr_bytes + kSlots * (x_bytes + c_bytes + s_bytes), &base))) return rc;
+  char* p = reinterpret_cast<char*>(base);
+  char* d_left = p;
+  char* d_right = p + (size_t)m * m * esz;
+  p += lr_bytes;
+  QO_CUDA_TRY(cudaMemcpyAsync(d_left, left_host, (size_t)m * m * esz, cudaMemcpyHostToDevice, streams[dev][0]));
+  QO_CUDA_TRY(cudaMemcpyAsync(d_right, right_host, (size_t)n * n * esz, cudaMemcpyHostToDevice, streams[dev][0]));
+  QO_CUDA_TRY(cudaStreamSynchronize(streams[dev][0]));
+
+  int slot = 0;
+  for (int64_t t0 = 0; t0 < tokens; t0 += slice, slot = (slot + 1) % kSlots) {
+    const int64_t cnt = (tokens - t0 < slice) ? tokens - t0 : slice;
+    char* dx = p + slot * (x_bytes + c_bytes + s_bytes);
+    char* dc = dx + x_bytes;
+    char* ds = dc + c_bytes;
+    cudaStream_t st = streams[dev][slot];
+    QO_CUDA_TRY(cudaMemcpyAsync(dx, reinterpret_cast<const char*>(x_host) + (size_t)t0 * feat * esz,
+                                (size_t)cnt * feat * esz, cudaMemcpyHostToDevice, st));
+    rc = qo_flatquant_quantize(dx, (int64_t)feat, d_left, d_right, dc, ds, cnt, m, n, clip_ratio, in_dtype, pack_int32,
+                               scale_dtype, st);
+    if (rc) break;
+    QO_CUDA_TRY(cudaMemcpyAsync(reinterpret_cast<char*>(codes_host) + (size_t)t0 * code_row, dc, (size_t)cnt * code_row,
+                                cudaMemcpyDeviceToHost, st));
+    QO_CUDA_TRY(cudaMemcpyAsync(reinterpret_cast<char*>(scales_host) + (size_t)t0 * ssz, ds, (size_t)cnt * ssz,
+                                cudaMemcpyDeviceToHost, st));
+  }
+  for (int s = 0; s < kSlots; ++s) {
+    cudaError_t e = cudaStreamSynchronize(streams[dev][s]);
+    if (e != cudaSuccess && rc == QO_OK) rc = fail(QO_ERR_CUDA, "host-buffer quantizer: %s", cudaGetErrorString(e));
+  }
+  return rc;
+}
+
+int qo_release_workspaces(void) {
+  clear_error();
+  int rc = QO_OK, cur = 0;
+  if (cudaGetDevice(&cur) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return QO_OK;
+  }
+  for (Scratch* s : {&g_scratch, &g_host_staging}) {
+    std::lock_guard<std::mutex> lock(s->mu);
+    for (int d = 0; d < kMaxDevices; ++d) {
+      if (!s->ptr[d]) continue;
+      if (cudaSetDevice(d) == cudaSuccess) {
+        cudaDeviceSynchronize();
+        if (cudaFree(s->ptr[d]) != cudaSuccess) rc = fail(QO_ERR_CUDA, "cudaFree of a library workspace failed");
+      }
+      s->ptr[d] = nullptr;
+      s->bytes[d] = 0;
+    }
+  }
+  cudaSetDevice(cur);
+  return rc;
+}
+
+}  // extern "C"

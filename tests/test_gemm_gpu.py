@@ -1,0 +1,191 @@
+"""GPU parity of the packed-int4 GEMM, dequantize, pack/unpack, weight quantizer and the fused layer (C ABI)."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import (N, QD, abi_int4_matmul, abi_quantize, bits_to_f32, bits_to_torch, golden, lib, make_inputs, ptr,
+                     stream_ptr, t2f)
+from oracle import w4a4_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def rand_problem(t, k, n, seed):
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randint(-8, 8, (t, k), generator=g, dtype=torch.int8)
+    w = torch.randint(-8, 8, (n, k), generator=g, dtype=torch.int8)  # weight layout [n_out, K]
+    sa = torch.rand(t, generator=g) * 0.1 + 0.01
+    sb = torch.rand(n, generator=g) * 0.1 + 0.01
+    ap = torch.from_numpy(O.pack_int4_to_int32(a.numpy()))
+    wp = torch.from_numpy(O.pack_int4_to_int32(w.numpy()))  # [n, K/8]
+    return a, w, ap, wp, sa, sb
+
+
+def both_policies(fn):
+    """Runs fn(policy) for the generic kernel and, where the shape has one, the tcgen05 kernel."""
+    yield "generic", fn(1)
+    try:
+        res = fn(2)
+    except N.QuantOpsError as e:
+        assert e.status == N.QO_ERR_UNSUPPORTED
+        return
+    yield "tcgen05", res
+
+
+@pytest.mark.parametrize("name", ["gemm_64x512x96", "gemm_33x256x40"])
+def test_against_reference_fixtures(name):
+    g = golden(name)
+    a, b = torch.from_numpy(g["a_packed"]).to(DEV), torch.from_numpy(g["b_packed"]).to(DEV)
+    sa, sb = torch.from_numpy(g["scale_a"]).to(DEV), torch.from_numpy(g["scale_b"]).to(DEV)
+    for label, (out, acc) in both_policies(lambda p: abi_int4_matmul(a, b, sa, sb, "fp16", True, policy=p)):
+        np.testing.assert_array_equal(acc.cpu().numpy(), g["acc"], err_msg=label)
+        np.testing.assert_array_equal(t2f(out), bits_to_f32(g["out_bits"], "fp16"), err_msg=label)
+
+
+SHAPES = [(1, 64, 8), (1, 4096, 4096), (16, 14336, 512), (128, 256, 256), (129, 1000 * 8, 130), (300, 4096, 520),
+          (1024, 1024, 1024), (256, 14336, 4096), (77, 8, 5)]
+
+
+@pytest.mark.parametrize("t,k,n", SHAPES)
+@pytest.mark.parametrize("layout", ["weights_t_view", "reference_contiguous"])
+def test_accumulators_bit_exact_and_outputs(t, k, n, layout):
+    a, w, ap, wp, sa, sb = rand_problem(t, k, n, t * 7 + k + n)
+    acc_ref = O.int4_accumulators(ap.numpy(), wp.numpy().T)
+    apd, sad, sbd = ap.to(DEV), sa.to(DEV), sb.to(DEV)
+    bd = wp.to(DEV).t() if layout == "weights_t_view" else wp.to(DEV).t().contiguous()
+    for out_dtype in ("fp16", "bf16"):
+        ref = O.round_to((acc_ref.astype(np.float32) * sa.numpy()[:, None]) * sb.numpy()[None, :], out_dtype)
+        for label, (out, acc) in both_policies(lambda p: abi_int4_matmul(apd, bd, sad, sbd, out_dtype, True, policy=p)):
+            np.testing.assert_array_equal(acc.cpu().numpy(), acc_ref, err_msg=f"{label} accumulators")
+            np.testing.assert_array_equal(t2f(out), ref, err_msg=f"{label} outputs")
+
+
+def test_extreme_codes_do_not_overflow():
+    t, k, n = 64, 14336, 64
+    ap = torch.full((t, k // 8), 0, dtype=torch.int32)          # all nibbles 0 -> code -8
+    wp = torch.full((n, k // 8), 0, dtype=torch.int32)
+    one = torch.ones(max(t, n))
+    for label, (out, acc) in both_policies(lambda p: abi_int4_matmul(ap.to(DEV), wp.to(DEV).t(), one[:t].to(DEV) * 1e-3,
+                                                                     one[:n].to(DEV) * 1e-3, "fp16", True, policy=p)):
+        assert int(acc.min()) == int(acc.max()) == 64 * k
+
+
+def test_library_owned_workspace_and_too_small_workspace():
+    a, w, ap, wp, sa, sb = rand_problem(256, 4096, 256, 5)
+    apd, bd, sad, sbd = ap.to(DEV), wp.to(DEV).t(), sa.to(DEV), sb.to(DEV)
+    ref = abi_int4_matmul(apd, bd, sad, sbd, "fp16")
+    got = abi_int4_matmul(apd, bd, sad, sbd, "fp16", use_workspace=False)
+    assert torch.equal(ref, got)
+    need = lib.qo_int4_matmul_workspace_bytes(256, 4096, 256)
+    if need:
+        small = torch.empty(16, dtype=torch.uint8, device=DEV)
+        out = torch.empty(256, 256, dtype=torch.float16, device=DEV)
+        rc = lib.qo_int4_matmul(ptr(apd), 512, ptr(bd), bd.stride(0), bd.stride(1), ptr(sad), ptr(sbd), ptr(out), N.QO_F16,
+                                256, 4096, 256, None, ptr(small), 16, stream_ptr())
+        assert rc == N.QO_ERR_WORKSPACE
+
+
+def test_gemm_on_quantizer_output_full_size():
+    """4096 x 4096 x 4096 with A produced by the quantizer: exact accumulators on sampled rows, linearity in the scales."""
+    x, left, right = make_inputs(4096, 4096, "bf16", 20242, True)
+    aq, sa = abi_quantize(x.to(DEV), left.to(DEV), right.to(DEV), 0.9, True, "bf16")
+    g = torch.Generator().manual_seed(20243)
+    w = torch.randn(4096, 4096, generator=g) * 0.02
+    wq, sw = O.quantize_weights(w.numpy())
+    wp = torch.from_numpy(O.pack_int4_to_int32(wq)).to(DEV)
+    swd = torch.from_numpy(sw).to(DEV)
+    out, acc = abi_int4_matmul(aq, wp.t(), sa, swd, "fp16", True)
+    rows = np.random.default_rng(1).choice(4096, 96, replace=False)
+    acc_ref = O.int4_accumulators(aq.cpu().numpy()[rows], wp.cpu().numpy().T)
+    np.testing.assert_array_equal(acc.cpu().numpy()[rows], acc_ref)
+    ref = O.round_to((acc_ref.astype(np.float32) * t2f(sa)[rows, None]) * sw[None, :], "fp16")
+    np.testing.assert_array_equal(t2f(out)[rows], ref)
+    out2 = abi_int4_matmul(aq, wp.t(), sa * 2, swd, "fp16")
+    np.testing.assert_allclose(t2f(out2), 2 * t2f(out), rtol=2e-3, atol=1e-6)
+
+
+@pytest.mark.parametrize("packed", [False, True])
+@pytest.mark.parametrize("scale_dtype", ["fp32", "bf16", "fp16"])
+def test_dequantize(packed, scale_dtype):
+    g = torch.Generator().manual_seed(4)
+    codes = torch.randint(-8, 8, (37, 1024), generator=g, dtype=torch.int8)
+    scales = (torch.rand(37, generator=g) + 0.01).to({"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}[scale_dtype])
+    q = torch.from_numpy(O.pack_int4_to_int32(codes.numpy())) if packed else codes
+    out = torch.empty(37, 1024, device=DEV)
+    N.check(lib.qo_dequantize_int4(ptr(q.to(DEV)), ptr(scales.to(DEV)), ptr(out), 37, 1024, int(packed), QD[scale_dtype], stream_ptr()))
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(out.cpu().numpy(), O.dequantize_int4(q.numpy(), t2f(scales), packed))
+
+
+def test_dequantize_reference_fixture_and_odd_width():
+    g = golden("quant_bf16_4096_packed")
+    out = torch.empty(2, 4096, device=DEV)
+    N.check(lib.qo_dequantize_int4(ptr(torch.from_numpy(g["codes"][:2].copy()).to(DEV)), ptr(torch.from_numpy(g["scales"][:2].copy()).to(DEV)),
+                                   ptr(out), 2, 4096, 1, N.QO_F32, stream_ptr()))
+    np.testing.assert_array_equal(out.cpu().numpy(), g["dequant_head"])
+    codes = torch.randint(-8, 8, (5, 15), dtype=torch.int8)
+    s = torch.rand(5) + 0.5
+    out = torch.empty(5, 15, device=DEV)
+    N.check(lib.qo_dequantize_int4(ptr(codes.to(DEV)), ptr(s.to(DEV)), ptr(out), 5, 15, 0, N.QO_F32, stream_ptr()))
+    np.testing.assert_array_equal(out.cpu().numpy(), O.dequantize_int4(codes.numpy(), s.numpy(), False))
+
+
+def test_pack_unpack_and_weight_quantizer():
+    g = torch.Generator().manual_seed(6)
+    codes = torch.randint(-8, 8, (100, 4096), generator=g, dtype=torch.int8)
+    packed = torch.empty(100, 512, dtype=torch.int32, device=DEV)
+    N.check(lib.qo_pack_int4(ptr(codes.to(DEV)), ptr(packed), 100, 4096, stream_ptr()))
+    np.testing.assert_array_equal(packed.cpu().numpy(), O.pack_int4_to_int32(codes.numpy()))
+    back = torch.empty(100, 4096, dtype=torch.int8, device=DEV)
+    N.check(lib.qo_unpack_int4(ptr(packed), ptr(back), 100, 4096, stream_ptr()))
+    assert torch.equal(back.cpu(), codes)
+    w = torch.randn(300, 1024, generator=g) * 0.02
+    w[7] = 0
+    wp = torch.empty(300, 128, dtype=torch.int32, device=DEV)
+    sw = torch.empty(300, device=DEV)
+    N.check(lib.qo_quantize_weights_int4(ptr(w.to(DEV)), ptr(wp), ptr(sw), 300, 1024, stream_ptr()))
+    wq_ref, sw_ref = O.quantize_weights(w.numpy())
+    np.testing.assert_array_equal(sw.cpu().numpy(), sw_ref)
+    np.testing.assert_array_equal(O.unpack_int32_to_int4(wp.cpu().numpy()), wq_ref)
+
+
+def abi_linear(x, left, right, wp, sw, bias, clip, dtype, out_dtype):
+    tokens, k = x.shape
+    n_out = wp.shape[0]
+    out = torch.empty(tokens, n_out, dtype={"fp16": torch.float16, "bf16": torch.bfloat16}[out_dtype], device=DEV)
+    need = lib.qo_w4a4_linear_workspace_bytes(tokens, k, n_out)
+    ws = torch.empty(need, dtype=torch.uint8, device=DEV)
+    N.check(lib.qo_w4a4_linear(ptr(x), x.stride(0), ptr(left), ptr(right), ptr(wp), ptr(sw), ptr(bias), ptr(out), tokens,
+                               left.shape[0], right.shape[0], n_out, clip, QD[dtype], QD[out_dtype], ptr(ws), need, stream_ptr()))
+    torch.cuda.synchronize()
+    return out
+
+
+def test_fused_layer_reference_fixture():
+    g = golden("linear_bf16_1024x48")
+    x, left, right = (bits_to_torch(g[k], "bf16").to(DEV) for k in ("x", "left", "right"))
+    out = abi_linear(x, left, right, torch.from_numpy(g["w_packed"]).to(DEV), torch.from_numpy(g["w_scale"]).to(DEV), None,
+                     float(g["clip"]), "bf16", "fp16")
+    ref = bits_to_f32(g["out_bits"], "fp16")
+    err = np.abs(t2f(out) - ref)
+    tol = 1e-2 * np.maximum(np.abs(ref), np.abs(ref).max(axis=1, keepdims=True) * 1e-2)
+    assert (err <= tol).mean() > 0.999
+
+
+@pytest.mark.parametrize("tokens", [1, 16, 256])
+def test_fused_layer_down_proj_shape(tokens):
+    x, left, right = make_inputs(tokens, 14336, "bf16", 20244 + tokens, True)
+    g = torch.Generator().manual_seed(20245)
+    w = torch.randn(4096, 14336, generator=g) * 0.02
+    wq, sw = O.quantize_weights(w.numpy())
+    wp = O.pack_int4_to_int32(wq)
+    bias = (torch.randn(4096, generator=g) * 0.1).bfloat16()
+    out = abi_linear(x.to(DEV), left.to(DEV), right.to(DEV), torch.from_numpy(wp).to(DEV), torch.from_numpy(sw).to(DEV),
+                     bias.to(DEV), 0.9, "bf16", "bf16")
+    # oracle with the GPU's own codes isolates the GEMM; with the oracle's codes it checks the whole layer
+    ref = O.w4a4_linear(t2f(x), t2f(left), t2f(right), 0.9, wp, sw, "bf16", "bf16")
+    ref = O.round_to(ref + t2f(bias)[None, :], "bf16")
+    got = t2f(out)
+    scale = np.abs(ref).max(axis=1, keepdims=True)
+    assert (np.abs(got - ref) <= 1e-2 * np.maximum(np.abs(ref), 0.05 * scale)).mean() > 0.995

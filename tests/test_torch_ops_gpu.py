@@ -1,0 +1,71 @@
+"""The Python / torch-dispatcher layer on the GPU: same calls a user of the reference makes."""
+import numpy as np
+import pytest
+import torch
+
+import quant_ops_b200 as q
+from helpers import compare_codes, compare_scales, make_inputs, t2f
+from oracle import w4a4_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def test_quantize_dequantize_matmul_chain():
+    x, left, right = make_inputs(200, 4096, "bf16", 31, True)
+    xd, ld, rd = x.to(DEV), left.to(DEV), right.to(DEV)
+    codes, scales = q.flatquant_dynamic_quantize(xd, ld, rd, 0.9, True)
+    assert codes.shape == (200, 512) and codes.dtype == torch.int32 and scales.shape == (200,) and scales.dtype == torch.float32
+    rc, rs = O.flatquant_quantize(t2f(x), t2f(left), t2f(right), 0.9, True, "bf16")
+    compare_scales(t2f(scales), rs)
+    compare_codes(O.unpack_int32_to_int4(codes.cpu().numpy()), O.unpack_int32_to_int4(rc))
+    c8, s8 = q.flatquant_dynamic_quantize(xd.view(200, 64, 64), ld, rd, 0.9, False)   # [T, M, N] input is accepted
+    assert c8.shape == (200, 4096) and c8.dtype == torch.int8
+    d_packed = q.dequantize_int4(codes, scales, True)
+    d_int8 = q.dequantize_int4(c8, s8, False)
+    assert d_packed.dtype == torch.float32 and torch.equal(d_packed, d_int8)          # packing loses nothing
+    w = torch.randn(96, 4096, generator=torch.Generator().manual_seed(2)) * 0.02
+    wp, sw = q.quantize_weights_int4(w.to(DEV))
+    out = q.int4_matmul(codes, wp.t(), scales, sw)
+    assert out.shape == (200, 96) and out.dtype == torch.float16
+    ref = O.int4_matmul(codes.cpu().numpy(), wp.cpu().numpy().T, t2f(scales), t2f(sw), "fp16")
+    np.testing.assert_array_equal(t2f(out), ref)
+    fused = q.w4a4_linear(xd, ld, rd, wp, sw, None, 0.9, torch.float16)
+    assert torch.equal(fused, out)
+    out_bf, acc = q.int4_matmul_ex(codes, wp.t().contiguous(), scales, sw, torch.bfloat16, True)
+    np.testing.assert_array_equal(acc.cpu().numpy(), O.int4_accumulators(codes.cpu().numpy(), wp.cpu().numpy().T))
+    assert torch.equal(q.unpack_int32_to_int4(q.pack_int4_to_int32(c8)), c8)
+
+
+def test_errors_are_raised_not_swallowed():
+    x, left, right = make_inputs(8, 256, "fp16", 3, False)
+    xd, ld, rd = x.to(DEV), left.to(DEV), right.to(DEV)
+    with pytest.raises(RuntimeError, match="must equal M\\*N"):
+        q.flatquant_dynamic_quantize(xd[:, :128], ld, rd)
+    with pytest.raises(RuntimeError, match="dtype"):
+        q.flatquant_dynamic_quantize(xd, ld.float(), rd)
+    with pytest.raises(RuntimeError, match="float32"):
+        q.int4_matmul(torch.zeros(2, 4, dtype=torch.int32, device=DEV), torch.zeros(4, 2, dtype=torch.int32, device=DEV),
+                      torch.ones(2, device=DEV, dtype=torch.float16), torch.ones(2, device=DEV))
+    with pytest.raises(RuntimeError, match="mismatch"):
+        q.int4_matmul(torch.zeros(2, 4, dtype=torch.int32, device=DEV), torch.zeros(5, 2, dtype=torch.int32, device=DEV),
+                      torch.ones(2, device=DEV), torch.ones(2, device=DEV))
+
+
+def test_runs_on_a_side_stream_and_in_a_cuda_graph():
+    x, left, right = make_inputs(64, 4096, "bf16", 5, True)
+    xd, ld, rd = x.to(DEV), left.to(DEV), right.to(DEV)
+    ref_c, ref_s = q.flatquant_dynamic_quantize(xd, ld, rd, 0.9, True)
+    st = torch.cuda.Stream()
+    st.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(st):
+        c, s = q.flatquant_dynamic_quantize(xd, ld, rd, 0.9, True)
+    st.synchronize()
+    assert torch.equal(c, ref_c) and torch.equal(s, ref_s)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        gc, gs = q.flatquant_dynamic_quantize(xd, ld, rd, 0.9, True)
+    xd.copy_(torch.roll(xd, 1, 0))
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(gc, torch.roll(ref_c, 1, 0)) and torch.equal(gs, torch.roll(ref_s, 1, 0))
