@@ -44,7 +44,7 @@ def make_inputs(tokens, seed):
     x[:, idx] *= 50
     left = torch.linalg.qr(torch.randn(M, M, dtype=torch.float64, generator=g)).Q
     right = torch.linalg.qr(torch.randn(N_, N_, dtype=torch.float64, generator=g)).Q
-    return x.bfloat16(), left.bfloat16(), right.bfloat16()
+    return x.bfloat16().contiguous(), left.bfloat16().contiguous(), right.bfloat16().contiguous()
 
 
 def measured_peak():

@@ -85,6 +85,21 @@ QO_API int qo_flatquant_quantize(const void* x, int64_t ldx, const void* left, c
                                  void* stream);
 
 /*
+ * The Kronecker transform alone: z[t] = round(L^T . round(X[t] . R)) as float32 [tokens, m*n] (values are
+ * representable in in_dtype).  Stands in for the first two lines of cuda_kronecker_quant_int8,
+ * src/quant_ops/ops/quantization/flatquant/kernels/cuda_quant_kernel.cu:337-339 (oracle: flatquant/ops.py:99-103).
+ */
+QO_API int qo_flatquant_transform(const void* x, int64_t ldx, const void* left, const void* right, float* z,
+                                  int64_t tokens, int m, int n, int in_dtype, void* stream);
+
+/*
+ * Synchronises `stream` and reports whether any kernel of this library gave up on a bounded device-side wait
+ * since the last call (QO_ERR_DEVICE_TIMEOUT, and the flag is cleared) -- the reference's counterpart is the
+ * cudaGetLastError check after its per-call synchronise, cuda_quant_kernel.cu:380-387.
+ */
+QO_API int qo_device_status(void* stream);
+
+/*
  * int4 codes (int8 or packed) times per-token scale -> float32 [tokens, features].
  * Stands in for: dequantize_int4, src/quant_ops/ops/quantization/flatquant/ops.py:156-178.
  */

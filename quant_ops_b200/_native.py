@@ -26,6 +26,8 @@ PROTOTYPES = {
     "qo_last_error": (C.c_char_p, []),
     "qo_get_decompose_dim": (_int, [_i64, C.POINTER(_i64), C.POINTER(_i64)]),
     "qo_flatquant_quantize": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _i64, _int, _int, _f32, _int, _int, _int, _vp]),
+    "qo_flatquant_transform": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _int, _int, _int, _vp]),
+    "qo_device_status": (_int, [_vp]),
     "qo_dequantize_int4": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _int, _vp]),
     "qo_int4_matmul_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "qo_int4_matmul": (_int, [_vp, _i64, _vp, _i64, _i64, _vp, _vp, _vp, _int, _i64, _i64, _i64, _vp, _vp, _sz, _vp]),
@@ -51,7 +53,7 @@ class QuantOpsError(RuntimeError):
 
 def _load_lib() -> C.CDLL:
     if not os.path.exists(LIB_PATH):
-        raise ImportError(f"{LIB_PATH} is missing: build it with `python -m quant_ops_b200.build` "
+        raise ImportError(f"{LIB_PATH} is missing: build it with `python quant_ops_b200/build.py` "
                           "(this package has no fallback implementation)")
     lib = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
     for name, (res, args) in PROTOTYPES.items():
@@ -77,7 +79,7 @@ def load_torch_binding() -> None:
     if _binding_loaded:
         return
     if not os.path.exists(BINDING_PATH):
-        raise ImportError(f"{BINDING_PATH} is missing: build it with `python -m quant_ops_b200.build`")
+        raise ImportError(f"{BINDING_PATH} is missing: build it with `python quant_ops_b200/build.py`")
     import torch
 
     torch.ops.load_library(BINDING_PATH)

@@ -1,7 +1,7 @@
 """Build recipe for the native parts: the C-ABI library and the thin torch binding.
 
-    python -m quant_ops_b200.build            # both
-    python -m quant_ops_b200.build --lib      # libquant_ops_b200.so only (nvcc, seconds)
+    python quant_ops_b200/build.py            # both
+    python quant_ops_b200/build.py --lib      # libquant_ops_b200.so only (nvcc, seconds)
 
 Everything is built in-tree, for sm_100a only.  No GPU is needed to build.
 """

@@ -153,7 +153,7 @@ int qo_flatquant_quantize(const void* x, int64_t ldx, const void* left, const vo
   if (tokens == 0) return QO_OK;
   if ((rc = require_device(nullptr))) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const bool fast_ok = flatquant_sm100_supported(ldx, m, n, in_dtype, x);
+  const bool fast_ok = flatquant_sm100_supported(ldx, m, n, in_dtype, x, clip_ratio);
   if (t_policy == 2 && !fast_ok)
     return fail(QO_ERR_UNSUPPORTED, "flatquant: no tcgen05 kernel for m=%d n=%d dtype=%d ldx=%lld", m, n, in_dtype, (long long)ldx);
   if (fast_ok && t_policy != 1) {
@@ -162,8 +162,41 @@ int qo_flatquant_quantize(const void* x, int64_t ldx, const void* left, const vo
                                   scale_dtype, st);
   }
   t_quant_path = 1;
-  return launch_flatquant_generic(x, ldx, left, right, codes, scales, tokens, m, n, clip_ratio, in_dtype, pack_int32,
+  return launch_flatquant_generic(x, ldx, left, right, codes, scales, tokens, m, n, clip_ratio, in_dtype, pack_int32 ? 1 : 0,
                                   scale_dtype, st);
+}
+
+int qo_flatquant_transform(const void* x, int64_t ldx, const void* left, const void* right, float* z, int64_t tokens,
+                           int m, int n, int in_dtype, void* stream) {
+  clear_error();
+  int rc = check_quant_args(x, ldx, left, right, z, z, tokens, m, n, in_dtype, 0, QO_F32);
+  if (rc) return rc;
+  if (tokens == 0) return QO_OK;
+  if ((rc = require_device(nullptr))) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const bool fast_ok = flatquant_sm100_supported(ldx, m, n, in_dtype, x, 1.0f);
+  if (t_policy == 2 && !fast_ok)
+    return fail(QO_ERR_UNSUPPORTED, "flatquant_transform: no tcgen05 kernel for m=%d n=%d dtype=%d", m, n, in_dtype);
+  if (fast_ok && t_policy != 1) {
+    t_quant_path = 2;
+    return launch_flatquant_sm100_mode(2, x, ldx, left, right, z, nullptr, tokens, m, n, 1.0f, in_dtype, QO_F32, st);
+  }
+  t_quant_path = 1;
+  return launch_transform_generic(x, ldx, left, right, z, tokens, m, n, in_dtype, st);
+}
+
+int qo_device_status(void* stream) {
+  clear_error();
+  int dev = 0, rc = require_device(&dev);
+  if (rc) return rc;
+  QO_CUDA_TRY(cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream)));
+  uint32_t* word = device_status_word(dev);
+  if (!word) return QO_OK;
+  uint32_t code = 0;
+  QO_CUDA_TRY(cudaMemcpy(&code, word, sizeof code, cudaMemcpyDeviceToHost));
+  if (code == 0) return QO_OK;
+  QO_CUDA_TRY(cudaMemset(word, 0, sizeof code));
+  return fail(QO_ERR_DEVICE_TIMEOUT, "a kernel gave up waiting (site 0x%x); its outputs are not valid", code);
 }
 
 int qo_dequantize_int4(const void* codes, const void* scales, float* out, int64_t tokens, int64_t features,

@@ -15,7 +15,8 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kRowsPerItem = 8;
 
-template <typename T, bool PACK>
+// MODE 0: int8 codes, 1: packed codes, 2: transform only (float32 Z written to `codes`)
+template <typename T, int MODE>
 __global__ void __launch_bounds__(kThreads)
 flatquant_generic_kernel(const T* __restrict__ x, int64_t ldx, const T* __restrict__ left,
                          const T* __restrict__ right, void* __restrict__ codes, void* __restrict__ scales,
@@ -81,6 +82,13 @@ flatquant_generic_kernel(const T* __restrict__ x, int64_t ldx, const T* __restri
         }
       }
     }
+    if (MODE == 2) {
+      __syncthreads();
+      float* zout = reinterpret_cast<float*>(codes) + tok * (int64_t)feat;
+      for (int i = tid; i < feat; i += kThreads) zout[i] = bufx[i];
+      __syncthreads();
+      continue;
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       lmin = fminf(lmin, __shfl_xor_sync(0xffffffffu, lmin, o));
@@ -104,7 +112,7 @@ flatquant_generic_kernel(const T* __restrict__ x, int64_t ldx, const T* __restri
     __syncthreads();
     const float s = s_scale;
 
-    if (PACK) {
+    if (MODE == 1) {
       int32_t* out = reinterpret_cast<int32_t*>(codes) + tok * (int64_t)(feat / 8);
       for (int p = tid; p < feat / 8; p += kThreads) {
         uint32_t w = 0;
@@ -130,7 +138,7 @@ int launch_typed(const void* x, int64_t ldx, const void* left, const void* right
   QO_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const int per_sm = smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : 4);
   const int grid = (int)(tokens < (int64_t)sms * per_sm ? tokens : (int64_t)sms * per_sm);
-  auto kern = pack ? flatquant_generic_kernel<T, true> : flatquant_generic_kernel<T, false>;
+  auto kern = pack == 2 ? flatquant_generic_kernel<T, 2> : (pack ? flatquant_generic_kernel<T, 1> : flatquant_generic_kernel<T, 0>);
   QO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   kern<<<grid, kThreads, smem, stream>>>(reinterpret_cast<const T*>(x), ldx, reinterpret_cast<const T*>(left),
                                           reinterpret_cast<const T*>(right), codes, scales, tokens, m, n, clip,
@@ -153,6 +161,11 @@ int launch_flatquant_generic(const void* x, int64_t ldx, const void* left, const
                                          stream);
   }
   return fail(QO_ERR_INVALID_ARGUMENT, "flatquant: unknown in_dtype %d", in_dtype);
+}
+
+int launch_transform_generic(const void* x, int64_t ldx, const void* left, const void* right, float* z, int64_t tokens,
+                             int m, int n, int in_dtype, cudaStream_t stream) {
+  return launch_flatquant_generic(x, ldx, left, right, z, z, tokens, m, n, 1.0f, in_dtype, 2, QO_F32, stream);
 }
 
 }  // namespace qo

@@ -19,8 +19,8 @@ constexpr int kLd = 17;          // unpacked words per row in smem (16 + 1 pad)
 __device__ __forceinline__ void widen(uint32_t w, uint32_t& lo, uint32_t& hi) {
   const uint32_t even = w & 0x0F0F0F0Fu, odd = (w >> 4) & 0x0F0F0F0Fu;
   const uint32_t l = __byte_perm(even, odd, 0x5140), h = __byte_perm(even, odd, 0x7362);
-  lo = ((l ^ 0x88888888u) - 0x08080808u) ^ 0x80808080u;  // per byte: v - 8, no borrow across bytes
-  hi = ((h ^ 0x88888888u) - 0x08080808u) ^ 0x80808080u;
+  lo = ((l | 0x80808080u) - 0x08080808u) ^ 0x80808080u;  // per byte: v - 8, no borrow across bytes
+  hi = ((h | 0x80808080u) - 0x08080808u) ^ 0x80808080u;
 }
 
 template <typename OutT>

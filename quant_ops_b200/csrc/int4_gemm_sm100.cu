@@ -1,7 +1,370 @@
+// Packed-int4 GEMM for sm_100a.
+//
+// Two steps on the caller's stream:
+//   1. widen: each packed operand is rewritten once as signed bytes, K contiguous (A8 [T, K], B8 [Nout, K]), into
+//      the workspace.  Doing this in a pass of its own keeps the GEMM main loop free of ALU work and of extra
+//      shared-memory traffic; the bytes written stay in the 126 MB L2 for the GEMM that follows.
+//   2. GEMM: persistent CTAs, one 128 x BN output tile at a time.  Warp 0 streams 128-byte-wide K slices of A8 and
+//      B8 with TMA (128-byte swizzle) through a ring of shared-memory stages, warp 1 issues tcgen05.mma kind::i8
+//      (int8 x int8 -> int32) into tensor memory, warps 2-5 read the accumulators back, apply
+//      (float(acc) * scale_a[row]) * scale_b[col] and store fp16 / bf16.  Two accumulator stages in tensor memory
+//      let the epilogue of one tile overlap the main loop of the next.
+//
+// Arithmetic is that of the reference kernel (src/quant_ops/ops/quantization/int4_matmul/kernels/
+// cuda_int4_matmul_kernel.cu:104-116): exact int32 accumulation, then the two float32 multiplies in that order.
+// Every mbarrier wait is bounded; a wait that runs out records a code in the device status word.
+#include <mutex>
+
 #include "qo_internal.cuh"
+#include "sm100_ptx.cuh"
+
 namespace qo {
-size_t gemm_sm100_workspace_bytes(int64_t, int64_t, int64_t) { return 0; }
-bool gemm_sm100_supported(int64_t, int64_t, int64_t, int64_t, int64_t, int64_t) { return false; }
-int launch_gemm_sm100(const int32_t*, int64_t, const int32_t*, int64_t, int64_t, const float*, const float*, void*, int,
-                      int64_t, int64_t, int64_t, int32_t*, const void*, void*, size_t, cudaStream_t) { return QO_ERR_UNSUPPORTED; }
+namespace {
+
+using namespace ptx;
+
+constexpr int kBM = 128;       // rows per output tile
+constexpr int kBK = 128;       // K bytes per pipeline stage (one 128-byte swizzle atom)
+constexpr int kGemmThreads = 192;
+
+// ---- step 1: widen ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint2 widen8(uint32_t w) {
+  const uint32_t even = w & 0x0F0F0F0Fu, odd = (w >> 4) & 0x0F0F0F0Fu;
+  const uint32_t l = __byte_perm(even, odd, 0x5140), h = __byte_perm(even, odd, 0x7362);
+  return make_uint2(((l | 0x80808080u) - 0x08080808u) ^ 0x80808080u, ((h | 0x80808080u) - 0x08080808u) ^ 0x80808080u);
 }
+
+// rows of packed words with unit stride along K: out[r][8*kw .. 8*kw+7]
+__global__ void __launch_bounds__(256)
+widen_rows_kernel(const uint32_t* __restrict__ in, int64_t ld_words, uint2* __restrict__ out, int64_t rows, int64_t kwords) {
+  const int64_t total = rows * kwords;
+  for (int64_t i = blockIdx.x * 256LL + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
+    const int64_t r = i / kwords, kw = i - r * kwords;
+    out[i] = widen8(in[r * ld_words + kw]);
+  }
+}
+
+// reference B layout [K/8, N] with N contiguous: transpose 32 x 32 words through shared memory so that both the
+// reads (along N) and the writes (along K) are contiguous
+__global__ void __launch_bounds__(256)
+widen_transpose_kernel(const uint32_t* __restrict__ in, int64_t bsk, int64_t bsn, uint2* __restrict__ out, int64_t n,
+                       int64_t kwords) {
+  __shared__ uint2 tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  const int64_t n0 = (int64_t)blockIdx.x * 32, k0 = (int64_t)blockIdx.y * 32;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t kw = k0 + ty + 8 * i, col = n0 + tx;
+    uint32_t w = 0x88888888u;
+    if (kw < kwords && col < n) w = in[kw * bsk + col * bsn];
+    tile[ty + 8 * i][tx] = widen8(w);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t col = n0 + ty + 8 * i, kw = k0 + tx;
+    if (col < n && kw < kwords) out[col * kwords + kw] = tile[tx][ty + 8 * i];
+  }
+}
+
+// ---- step 2: GEMM --------------------------------------------------------------------------------------------
+template <int BN>
+struct GemmCfg {
+  static constexpr int kStageBytes = (kBM + BN) * kBK;
+  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kOffSb = kStages * kStageBytes;           // 4 warps x BN floats
+  static constexpr int kOffBar = kOffSb + 4 * BN * 4;
+  static constexpr int kSmemBytes = kOffBar + 256 + 1024;
+  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+};
+
+struct GemmBars {
+  uint64_t full[8], empty[8], acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+};
+
+template <typename OutT>
+__device__ __forceinline__ uint32_t pack_out2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack_out2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack_out2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ float2 unpack_out2(uint32_t w, __half) {
+  return __half22float2(*reinterpret_cast<__half2*>(&w));
+}
+__device__ __forceinline__ float2 unpack_out2(uint32_t w, __nv_bfloat16) {
+  return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&w));
+}
+
+template <int BN, typename OutT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
+                     const float* __restrict__ sa, const float* __restrict__ sb, OutT* __restrict__ out,
+                     int32_t* __restrict__ acc_out, const OutT* __restrict__ bias, int t, int n, int k,
+                     uint32_t* __restrict__ status) {
+  using C = GemmCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  GemmBars* bars = reinterpret_cast<GemmBars*>(smem + C::kOffBar);
+  const uint32_t smem_base = smem_u32(smem);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tiles_n = (n + BN - 1) / BN, tiles_m = (t + kBM - 1) / kBM;
+  const int ntiles = tiles_m * tiles_n, ksteps = (k + kBK - 1) / kBK;
+
+  if (tid == 0) {
+    for (int i = 0; i < C::kStages; ++i) { mbar_init(smem_u32(&bars->full[i]), 1); mbar_init(smem_u32(&bars->empty[i]), 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&bars->acc_full[i]), 1); mbar_init(smem_u32(&bars->acc_empty[i]), 128); }
+    fence_barrier_init();
+    prefetch_tensormap(&a_map);
+    prefetch_tensormap(&b_map);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&bars->tmem_base), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int step = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < ntiles; tile += gridDim.x) {
+        const int mb = tile / tiles_n, nb = tile - mb * tiles_n;
+        for (int ks = 0; ks < ksteps; ++ks, ++step) {
+          const int s = step % C::kStages, ph = (step / C::kStages) & 1;
+          if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1)) { atomicCAS(status, 0u, 0x500u + s); ok = false; break; }
+          const uint32_t bar = smem_u32(&bars->full[s]);
+          mbar_arrive_expect_tx(bar, C::kStageBytes);
+          const uint32_t dst = smem_base + s * C::kStageBytes;
+          tma_load_2d(dst, &a_map, bar, ks * kBK, mb * kBM);
+          tma_load_2d(dst + kBM * kBK, &b_map, bar, ks * kBK, nb * BN);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(2, 1, 1, 0, 0, kBM, BN);  // s32 accumulators, s8 x s8, both K-major
+      int step = 0, lt = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < ntiles; tile += gridDim.x, ++lt) {
+        const int as = lt & 1, aph = (lt >> 1) & 1;
+        if (!mbar_wait(smem_u32(&bars->acc_empty[as]), aph ^ 1)) { atomicCAS(status, 0u, 0x510u + as); break; }
+        tc_fence_after();
+        for (int ks = 0; ks < ksteps; ++ks, ++step) {
+          const int s = step % C::kStages, ph = (step / C::kStages) & 1;
+          if (!mbar_wait(smem_u32(&bars->full[s]), ph)) { atomicCAS(status, 0u, 0x520u + s); ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_base = smem_base + s * C::kStageBytes, b_base = a_base + kBM * kBK;
+#pragma unroll
+          for (int j = 0; j < kBK / 32; ++j) {
+            const uint64_t ad = umma_smem_desc_sw128(a_base + j * 32, 16, 1024);
+            const uint64_t bd = umma_smem_desc_sw128(b_base + j * 32, 16, 1024);
+            mma_i8_ss(tmem + as * BN, ad, bd, idesc, (ks | j) != 0);
+          }
+          mma_commit(smem_u32(&bars->empty[s]));
+        }
+        if (ok) mma_commit(smem_u32(&bars->acc_full[as]));
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    float* sb_s = reinterpret_cast<float*>(smem + C::kOffSb) + (warp - 2) * BN;
+    int lt = 0;
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++lt) {
+      const int mb = tile / tiles_n, nb = tile - mb * tiles_n;
+      const int as = lt & 1, aph = (lt >> 1) & 1;
+      const int row = mb * kBM + q * 32 + lane;
+      const bool row_ok = row < t;
+      const float s_row = row_ok ? sa[row] : 0.f;
+      __syncwarp();
+      for (int i = lane; i < BN; i += 32) sb_s[i] = (nb * BN + i < n) ? sb[nb * BN + i] : 0.f;
+      __syncwarp();
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->acc_full[as]), aph))) { atomicCAS(status, 0u, 0x530u + as); break; }
+      tc_fence_after();
+#pragma unroll 2
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + as * BN + c0, v);
+        tmem_ld_wait();
+        const int col0 = nb * BN + c0;
+        if (row_ok && col0 < n) {
+          uint32_t w[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float f0 = ((float)(int)v[2 * j] * s_row) * sb_s[c0 + 2 * j];
+            const float f1 = ((float)(int)v[2 * j + 1] * s_row) * sb_s[c0 + 2 * j + 1];
+            w[j] = pack_out2<OutT>(f0, f1);
+          }
+          OutT* orow = out + (int64_t)row * n + col0;
+          if (bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (col0 + 2 * j < n) {
+                const float2 o = unpack_out2(w[j], OutT());
+                const float2 b = unpack_out2(*reinterpret_cast<const uint32_t*>(bias + col0 + 2 * j), OutT());
+                w[j] = pack_out2<OutT>(o.x + b.x, o.y + b.y);
+              }
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (col0 + 8 * j < n) reinterpret_cast<uint4*>(orow)[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+          if (acc_out != nullptr) {
+            int32_t* arow = acc_out + (int64_t)row * n + col0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (col0 + 4 * j < n) reinterpret_cast<uint4*>(arow)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bars->acc_empty[as]));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, C::kTmemCols);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn gemm_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    else
+      (void)cudaGetLastError();
+  });
+  return fn;
+}
+
+int make_map_s8(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int box_rows) {
+  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)k};
+  const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = gemm_encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(QO_ERR_CUDA, "int4_matmul: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return QO_OK;
+}
+
+template <int BN, typename OutT>
+int launch_gemm_tile(const int8_t* a8, const int8_t* b8, const float* sa, const float* sb, void* out, int32_t* acc_out,
+                     const void* bias, int64_t t, int64_t k, int64_t n, uint32_t* status, cudaStream_t stream) {
+  using C = GemmCfg<BN>;
+  CUtensorMap a_map, b_map;
+  int rc = make_map_s8(&a_map, a8, t, k, kBM);
+  if (rc) return rc;
+  if ((rc = make_map_s8(&b_map, b8, n, k, BN))) return rc;
+  auto kern = gemm_s8_sm100_kernel<BN, OutT>;
+  int dev = 0, sms = 148;
+  QO_CUDA_TRY(cudaGetDevice(&dev));
+  static bool configured[64] = {};
+  if (!configured[dev & 63]) {
+    QO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+    configured[dev & 63] = true;
+  }
+  QO_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int64_t ntiles = ((t + kBM - 1) / kBM) * ((n + BN - 1) / BN);
+  const int grid = (int)(ntiles < sms ? ntiles : sms);
+  kern<<<grid, kGemmThreads, C::kSmemBytes, stream>>>(a_map, b_map, sa, sb, reinterpret_cast<OutT*>(out), acc_out,
+                                                     reinterpret_cast<const OutT*>(bias), (int)t, (int)n, (int)k, status);
+  return check_launch("gemm_s8_sm100_kernel");
+}
+
+template <typename OutT>
+int launch_gemm_typed(const int8_t* a8, const int8_t* b8, const float* sa, const float* sb, void* out, int32_t* acc_out,
+                      const void* bias, int64_t t, int64_t k, int64_t n, uint32_t* status, cudaStream_t stream) {
+  // widest tile that does not leave most SMs idle
+  const int64_t tiles_m = (t + kBM - 1) / kBM;
+  if (n >= 256 && tiles_m * ((n + 255) / 256) >= 120)
+    return launch_gemm_tile<256, OutT>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream);
+  if (n >= 128 && tiles_m * ((n + 127) / 128) >= 100)
+    return launch_gemm_tile<128, OutT>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream);
+  return launch_gemm_tile<64, OutT>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream);
+}
+
+inline size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+}  // namespace
+
+size_t gemm_sm100_workspace_bytes(int64_t t, int64_t k, int64_t n) {
+  if (t <= 0 || k <= 0 || n <= 0) return 0;
+  return align256((size_t)t * k) + align256((size_t)n * k);
+}
+
+bool gemm_sm100_supported(int64_t t, int64_t k, int64_t n, int64_t lda, int64_t bsk, int64_t bsn) {
+  (void)lda;
+  if (k % 16 || k < 16) return false;              // TMA: row stride of the widened operands must be 16-byte aligned
+  if (n % 8) return false;                         // 16-byte output stores
+  if (t > 0x7fffff00LL || n > 0x7fffff00LL || k > 262143) return false;
+  if (bsk != 1 && bsn != 1) return false;
+  return gemm_encode_fn() != nullptr;
+}
+
+int launch_gemm_sm100_s8(const int8_t* a8, const int8_t* b8, const float* sa, const float* sb, void* out, int out_dtype,
+                         int64_t t, int64_t k, int64_t n, int32_t* acc_out, const void* bias, cudaStream_t stream) {
+  if (reinterpret_cast<uintptr_t>(a8) % 16 || reinterpret_cast<uintptr_t>(b8) % 16 || reinterpret_cast<uintptr_t>(out) % 16 ||
+      (acc_out && reinterpret_cast<uintptr_t>(acc_out) % 16) || (bias && reinterpret_cast<uintptr_t>(bias) % 4))
+    return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: operands of the tcgen05 kernel must be 16-byte aligned");
+  int dev = 0;
+  QO_CUDA_TRY(cudaGetDevice(&dev));
+  uint32_t* status = device_status_word(dev);
+  if (!status) return fail(QO_ERR_CUDA, "int4_matmul: could not allocate the device status word");
+  if (out_dtype == QO_F16) return launch_gemm_typed<__half>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream);
+  return launch_gemm_typed<__nv_bfloat16>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream);
+}
+
+int launch_widen_rows(const int32_t* in, int64_t ld_words, int8_t* out, int64_t rows, int64_t k, cudaStream_t stream) {
+  const int64_t total = rows * (k / 8);
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  widen_rows_kernel<<<(int)blocks, 256, 0, stream>>>(reinterpret_cast<const uint32_t*>(in), ld_words,
+                                                     reinterpret_cast<uint2*>(out), rows, k / 8);
+  return check_launch("widen_rows_kernel");
+}
+
+int launch_gemm_sm100(const int32_t* a, int64_t lda, const int32_t* b, int64_t bsk, int64_t bsn, const float* sa,
+                      const float* sb, void* out, int out_dtype, int64_t t, int64_t k, int64_t n, int32_t* acc_out,
+                      const void* bias, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  if (workspace_bytes < gemm_sm100_workspace_bytes(t, k, n) || reinterpret_cast<uintptr_t>(workspace) % 256)
+    return fail(QO_ERR_WORKSPACE, "int4_matmul: workspace missing, too small or not 256-byte aligned");
+  int8_t* a8 = reinterpret_cast<int8_t*>(workspace);
+  int8_t* b8 = a8 + align256((size_t)t * k);
+  int rc = launch_widen_rows(a, lda, a8, t, k, stream);
+  if (rc) return rc;
+  if (bsk == 1) {
+    rc = launch_widen_rows(b, bsn, b8, n, k, stream);  // rows of the weight matrix [Nout, K/8]
+  } else {
+    dim3 grid((unsigned)((n + 31) / 32), (unsigned)((k / 8 + 31) / 32));
+    widen_transpose_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const uint32_t*>(b), bsk, bsn,
+                                                     reinterpret_cast<uint2*>(b8), n, k / 8);
+    rc = check_launch("widen_transpose_kernel");
+  }
+  if (rc) return rc;
+  return launch_gemm_sm100_s8(a8, b8, sa, sb, out, out_dtype, t, k, n, acc_out, bias, stream);
+}
+
+}  // namespace qo

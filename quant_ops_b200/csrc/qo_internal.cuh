@@ -122,7 +122,15 @@ int launch_flatquant_generic(const void* x, int64_t ldx, const void* left, const
 int launch_flatquant_sm100(const void* x, int64_t ldx, const void* left, const void* right, void* codes,
                            void* scales, int64_t tokens, int m, int n, float clip, int in_dtype, int pack,
                            int scale_dtype, cudaStream_t stream);
-bool flatquant_sm100_supported(int64_t ldx, int m, int n, int in_dtype, const void* x);
+bool flatquant_sm100_supported(int64_t ldx, int m, int n, int in_dtype, const void* x, float clip);
+// mode: 0 int8 codes, 1 packed codes, 2 transform only (float32 Z written to `codes`)
+int launch_flatquant_sm100_mode(int mode, const void* x, int64_t ldx, const void* left, const void* right, void* codes,
+                                void* scales, int64_t tokens, int m, int n, float clip, int in_dtype, int scale_dtype,
+                                cudaStream_t stream);
+int launch_transform_generic(const void* x, int64_t ldx, const void* left, const void* right, float* z, int64_t tokens,
+                             int m, int n, int in_dtype, cudaStream_t stream);
+// device word that kernels set when a bounded wait runs out (nullptr if it could not be allocated)
+uint32_t* device_status_word(int dev);
 
 int launch_dequantize(const void* codes, const void* scales, float* out, int64_t tokens, int64_t features,
                       int packed, int scale_dtype, cudaStream_t stream);
@@ -140,5 +148,10 @@ int launch_gemm_sm100(const int32_t* a, int64_t lda, const int32_t* b, int64_t b
                       const float* sa, const float* sb, void* out, int out_dtype, int64_t t, int64_t k,
                       int64_t n, int32_t* acc_out, const void* bias, void* workspace, size_t workspace_bytes,
                       cudaStream_t stream);
+
+// pieces of the tcgen05 GEMM, used separately by the fused layer
+int launch_widen_rows(const int32_t* in, int64_t ld_words, int8_t* out, int64_t rows, int64_t k, cudaStream_t stream);
+int launch_gemm_sm100_s8(const int8_t* a8, const int8_t* b8, const float* sa, const float* sb, void* out, int out_dtype,
+                         int64_t t, int64_t k, int64_t n, int32_t* acc_out, const void* bias, cudaStream_t stream);
 
 }  // namespace qo

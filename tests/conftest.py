@@ -11,10 +11,10 @@ if ROOT not in sys.path:
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a B200 (sm_100) GPU; everything else runs on CPU")
     # the native pieces are build products (git-ignored): make sure they exist before anything imports the package
-    from quant_ops_b200 import build as qbuild
+    # (run as a script: importing the package would already need the library it builds)
+    import subprocess
 
-    qbuild.build_lib()
-    qbuild.build_torch_binding()
+    subprocess.run([sys.executable, os.path.join(ROOT, "quant_ops_b200", "build.py")], check=True)
 
 
 def pytest_collection_modifyitems(config, items):

@@ -56,7 +56,8 @@ def make_inputs(tokens, feat, dtype, seed, outliers=True, ortho=True, mn=None):
     else:
         left = torch.randn(m, m, generator=g)
         right = torch.randn(n, n, generator=g)
-    return x.to(TD[dtype]), left.to(TD[dtype]), right.to(TD[dtype])
+    # QR hands back column-major factors: the C ABI wants plain row-major buffers
+    return x.to(TD[dtype]).contiguous(), left.to(TD[dtype]).contiguous(), right.to(TD[dtype]).contiguous()
 
 
 def ptr(t):

@@ -30,6 +30,7 @@ def both_policies(fn):
     except N.QuantOpsError as e:
         assert e.status == N.QO_ERR_UNSUPPORTED
         return
+    assert lib.qo_device_status(stream_ptr()) == N.QO_OK, lib.qo_last_error()
     yield "tcgen05", res
 
 
@@ -113,7 +114,8 @@ def test_dequantize(packed, scale_dtype):
     scales = (torch.rand(37, generator=g) + 0.01).to({"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}[scale_dtype])
     q = torch.from_numpy(O.pack_int4_to_int32(codes.numpy())) if packed else codes
     out = torch.empty(37, 1024, device=DEV)
-    N.check(lib.qo_dequantize_int4(ptr(q.to(DEV)), ptr(scales.to(DEV)), ptr(out), 37, 1024, int(packed), QD[scale_dtype], stream_ptr()))
+    qd, sd = q.to(DEV), scales.to(DEV)  # keep the device buffers alive across the call
+    N.check(lib.qo_dequantize_int4(ptr(qd), ptr(sd), ptr(out), 37, 1024, int(packed), QD[scale_dtype], stream_ptr()))
     torch.cuda.synchronize()
     np.testing.assert_array_equal(out.cpu().numpy(), O.dequantize_int4(q.numpy(), t2f(scales), packed))
 
@@ -121,13 +123,14 @@ def test_dequantize(packed, scale_dtype):
 def test_dequantize_reference_fixture_and_odd_width():
     g = golden("quant_bf16_4096_packed")
     out = torch.empty(2, 4096, device=DEV)
-    N.check(lib.qo_dequantize_int4(ptr(torch.from_numpy(g["codes"][:2].copy()).to(DEV)), ptr(torch.from_numpy(g["scales"][:2].copy()).to(DEV)),
-                                   ptr(out), 2, 4096, 1, N.QO_F32, stream_ptr()))
+    cd, sd = torch.from_numpy(g["codes"][:2].copy()).to(DEV), torch.from_numpy(g["scales"][:2].copy()).to(DEV)
+    N.check(lib.qo_dequantize_int4(ptr(cd), ptr(sd), ptr(out), 2, 4096, 1, N.QO_F32, stream_ptr()))
     np.testing.assert_array_equal(out.cpu().numpy(), g["dequant_head"])
     codes = torch.randint(-8, 8, (5, 15), dtype=torch.int8)
     s = torch.rand(5) + 0.5
     out = torch.empty(5, 15, device=DEV)
-    N.check(lib.qo_dequantize_int4(ptr(codes.to(DEV)), ptr(s.to(DEV)), ptr(out), 5, 15, 0, N.QO_F32, stream_ptr()))
+    cd, sd = codes.to(DEV), s.to(DEV)
+    N.check(lib.qo_dequantize_int4(ptr(cd), ptr(sd), ptr(out), 5, 15, 0, N.QO_F32, stream_ptr()))
     np.testing.assert_array_equal(out.cpu().numpy(), O.dequantize_int4(codes.numpy(), s.numpy(), False))
 
 
@@ -135,7 +138,8 @@ def test_pack_unpack_and_weight_quantizer():
     g = torch.Generator().manual_seed(6)
     codes = torch.randint(-8, 8, (100, 4096), generator=g, dtype=torch.int8)
     packed = torch.empty(100, 512, dtype=torch.int32, device=DEV)
-    N.check(lib.qo_pack_int4(ptr(codes.to(DEV)), ptr(packed), 100, 4096, stream_ptr()))
+    codes_d = codes.to(DEV)
+    N.check(lib.qo_pack_int4(ptr(codes_d), ptr(packed), 100, 4096, stream_ptr()))
     np.testing.assert_array_equal(packed.cpu().numpy(), O.pack_int4_to_int32(codes.numpy()))
     back = torch.empty(100, 4096, dtype=torch.int8, device=DEV)
     N.check(lib.qo_unpack_int4(ptr(packed), ptr(back), 100, 4096, stream_ptr()))
@@ -144,7 +148,8 @@ def test_pack_unpack_and_weight_quantizer():
     w[7] = 0
     wp = torch.empty(300, 128, dtype=torch.int32, device=DEV)
     sw = torch.empty(300, device=DEV)
-    N.check(lib.qo_quantize_weights_int4(ptr(w.to(DEV)), ptr(wp), ptr(sw), 300, 1024, stream_ptr()))
+    w_d = w.to(DEV)
+    N.check(lib.qo_quantize_weights_int4(ptr(w_d), ptr(wp), ptr(sw), 300, 1024, stream_ptr()))
     wq_ref, sw_ref = O.quantize_weights(w.numpy())
     np.testing.assert_array_equal(sw.cpu().numpy(), sw_ref)
     np.testing.assert_array_equal(O.unpack_int32_to_int4(wp.cpu().numpy()), wq_ref)

@@ -31,6 +31,7 @@ def run_both(x, left, right, clip, pack, dtype):
         assert e.status == N.QO_ERR_UNSUPPORTED
         return
     assert lib.qo_last_quantizer_path() == 2
+    assert lib.qo_device_status(stream_ptr()) == N.QO_OK, lib.qo_last_error()
     yield "tcgen05", codes.cpu().numpy(), t2f(scales)
 
 
@@ -153,3 +154,26 @@ def test_host_buffer_entry_point():
                                            N.QO_BF16, 1, N.QO_F32))
     c_dev, s_dev = abi_quantize(x.to(DEV), left.to(DEV), right.to(DEV), 0.9, True, "bf16")
     assert torch.equal(codes, c_dev.cpu()) and torch.equal(scales, s_dev.cpu())
+
+
+@pytest.mark.parametrize("tokens,feat,dtype", [(5, 4096, "bf16"), (3, 14336, "fp16"), (4, 11008, "bf16"), (6, 256, "fp32")])
+def test_transform_entry_point(tokens, feat, dtype):
+    """The Kronecker transform alone, both kernels, against the oracle (a handful of 1-ulp roundings may differ:
+    the products are accumulated in a different order)."""
+    x, left, right = make_inputs(tokens, feat, dtype, 55, True)
+    ref = O.kronecker_transform(t2f(x), t2f(left), t2f(right), dtype)
+    xd, ld, rd = x.to(DEV), left.to(DEV), right.to(DEV)
+    for policy in (1, 2):
+        z = torch.empty(tokens, feat, device=DEV)
+        N.check(lib.qo_set_kernel_policy(policy))
+        rc = lib.qo_flatquant_transform(ptr(xd), feat, ptr(ld), ptr(rd), ptr(z), tokens, left.shape[0], right.shape[0],
+                                        QD[dtype], stream_ptr())
+        lib.qo_set_kernel_policy(0)
+        if rc == N.QO_ERR_UNSUPPORTED and policy == 2:
+            continue
+        N.check(rc)
+        assert lib.qo_device_status(stream_ptr()) == N.QO_OK
+        got = t2f(z)
+        ulp = {"bf16": 2.0 ** -7, "fp16": 2.0 ** -10, "fp32": 2.0 ** -20}[dtype]
+        assert np.all(np.abs(got - ref) <= ulp * np.maximum(np.abs(ref), 1e-3) * 1.01 + 1e-6)
+        assert (got != ref).mean() < 2e-2
