@@ -175,5 +175,6 @@ def test_transform_entry_point(tokens, feat, dtype):
         assert lib.qo_device_status(stream_ptr()) == N.QO_OK
         got = t2f(z)
         ulp = {"bf16": 2.0 ** -7, "fp16": 2.0 ** -10, "fp32": 2.0 ** -20}[dtype]
-        assert np.all(np.abs(got - ref) <= ulp * np.maximum(np.abs(ref), 1e-3) * 1.01 + 1e-6)
+        # a flipped rounding of Y moves Z by a fraction of Y's spacing, so the bound is relative to the row's range
+        assert np.all(np.abs(got - ref) <= ulp * np.abs(ref).max(axis=1, keepdims=True) * 1.01 + 1e-6)
         assert (got != ref).mean() < 2e-2
