@@ -80,18 +80,82 @@ __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// quotient z / s rounded to the activation dtype (see the file comment for the bf16 shortcut)
+// Two-wide arithmetic in the activation dtype, used by the quantize pass.  Everything here runs on the ALU / FMA
+// pipes (packed converts, packed min / max / add); none of it touches the conversion unit.
+//   cvt(lo, hi)      two float32 -> packed pair, round to nearest even
+//   lo(p), hi(p)     packed pair -> float32
+//   nibbles(q)       clamp both halves to [-8, 7], then add the constant whose spacing is 1 (200 for bf16, 1032 for
+//                    fp16): the sum is rint(q) + 8 with ties to even, and it sits in the low 4 bits of each half
+//   quot(z0, z1)     round(z / s) for both; bf16 multiplies by 1/s (exact, see the file comment), fp16 refines the
+//                    product with two FMAs, which gives the correctly rounded quotient (Markstein)
+template <typename T> struct P2;
+template <> struct P2<__nv_bfloat16> {
+  static constexpr uint32_t kByteMask = 0x0F0F0F0Fu;  // the nibble's byte also carries exponent bits
+  static __device__ __forceinline__ uint32_t cvt(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+  }
+  static __device__ __forceinline__ float lo(uint32_t p) { return __uint_as_float(p << 16); }
+  static __device__ __forceinline__ float hi(uint32_t p) { return __uint_as_float(p & 0xFFFF0000u); }
+  static __device__ __forceinline__ uint32_t nibbles(uint32_t q) {
+    uint32_t d;
+    asm("{\n\t.reg .b32 t;\n\t"
+        "max.bf16x2 t, %1, %2;\n\t"
+        "min.bf16x2 t, t, %3;\n\t"
+        "add.rn.bf16x2 %0, t, %4;\n\t}"
+        : "=r"(d) : "r"(q), "r"(0xC100C100u), "r"(0x40E040E0u), "r"(0x43484348u));
+    return d;
+  }
+  static __device__ __forceinline__ uint32_t quot(float z0, float z1, float, float inv_s) { return cvt(z0 * inv_s, z1 * inv_s); }
+};
+template <> struct P2<__half> {
+  static constexpr uint32_t kByteMask = 0xFFFFFFFFu;
+  static __device__ __forceinline__ uint32_t cvt(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+  }
+  static __device__ __forceinline__ float lo(uint32_t p) { return __low2float(*reinterpret_cast<__half2*>(&p)); }
+  static __device__ __forceinline__ float hi(uint32_t p) { return __high2float(*reinterpret_cast<__half2*>(&p)); }
+  static __device__ __forceinline__ uint32_t nibbles(uint32_t q) {
+    uint32_t d;
+    asm("{\n\t.reg .b32 t;\n\t"
+        "max.f16x2 t, %1, %2;\n\t"
+        "min.f16x2 t, t, %3;\n\t"
+        "add.rn.f16x2 %0, t, %4;\n\t}"
+        : "=r"(d) : "r"(q), "r"(0xC800C800u), "r"(0x47004700u), "r"(0x64086408u));
+    return d;
+  }
+  static __device__ __forceinline__ uint32_t quot(float z0, float z1, float s, float inv_s) {
+    float q0 = z0 * inv_s, q1 = z1 * inv_s;
+    q0 = fmaf(fmaf(-q0, s, z0), inv_s, q0);
+    q1 = fmaf(fmaf(-q1, s, z1), inv_s, q1);
+    return cvt(q0, q1);
+  }
+};
+
+// 32 accumulator values of one row -> 32 offset-binary nibbles, as 4 words of 4 bytes-with-a-nibble each pair
+// (P = elements 0..3, Q = elements 4..7 of a group of 8; see pack8 / bytes4)
 template <typename T>
-__device__ __forceinline__ float quotient(float z, float s, float inv_s);
-template <>
-__device__ __forceinline__ float quotient<__nv_bfloat16>(float z, float, float inv_s) {
-  return DT<__nv_bfloat16>::rnd(z * inv_s);
+__device__ __forceinline__ void nibble_bytes(const uint32_t (&v)[32], int base, float s, float inv_s, uint32_t& p, uint32_t& q) {
+  uint32_t t[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t zz = P2<T>::cvt(__uint_as_float(v[base + 2 * i]), __uint_as_float(v[base + 2 * i + 1]));  // round z
+    t[i] = P2<T>::nibbles(P2<T>::quot(P2<T>::lo(zz), P2<T>::hi(zz), s, inv_s));
+  }
+  p = __byte_perm(t[0], t[1], 0x6420) & P2<T>::kByteMask;  // bytes: elements 0, 1, 2, 3
+  q = __byte_perm(t[2], t[3], 0x6420) & P2<T>::kByteMask;  // bytes: elements 4, 5, 6, 7
 }
-template <>
-__device__ __forceinline__ float quotient<__half>(float z, float s, float) {
-  if (s == 0.f) return z > 0.f ? 7.f : (z < 0.f ? -8.f : 0.f);
-  return DT<__half>::rnd(__fdiv_rn(z, s));
+// 8 nibble-bytes -> one packed word, nibble i at bits 4i
+__device__ __forceinline__ uint32_t pack8(uint32_t p, uint32_t q) {
+  p |= p >> 4;
+  q |= q >> 4;
+  return __byte_perm(p, q, 0x6420);
 }
+// 4 nibble-bytes (offset binary) -> 4 signed bytes
+__device__ __forceinline__ uint32_t bytes4(uint32_t p) { return ((p | 0x80808080u) - 0x08080808u) ^ 0x80808080u; }
 
 __device__ __forceinline__ void report(uint32_t* status, Misc* misc, uint32_t code) {
   atomicCAS(status, 0u, code);
@@ -137,25 +201,34 @@ flatquant_sm100_kernel(const __grid_constant__ CUtensorMap x_map, const T* __res
     tmem_alloc(smem_u32(&misc->tmem_base), C::kTmemCols);
     tmem_relinquish();
   }
-  // R^T as a K-major operand: row = output column n, k runs along the row; 128-byte swizzle within 8-row groups
-  for (int idx = tid; idx < NDIM * NDIM; idx += kThreads) {
-    const int j = idx / NDIM, n = idx % NDIM;  // R[j][n]
-    const uint32_t off = (j >> 6) * (NDIM * 128) + (n >> 3) * 1024 + (n & 7) * 128 + ((((j & 63) >> 3) ^ (n & 7)) << 4) + (j & 7) * 2;
-    *reinterpret_cast<T*>(smem + C::kOffR + off) = right[idx];
-  }
-  // blockdiag(L^T): entry (row r = (g, i), column c = (g', k)) is L[k][i] when g == g', else 0
-  for (int idx = tid; idx < 128 * 128; idx += kThreads) {
-    const int r = idx >> 7, c = idx & 127;
-    T v = T(0.f);
-    if (r < rows_tile && c < rows_tile && (r / m) == (c / m)) v = left[(c % m) * m + (r % m)];
-    const uint32_t off = (c >> 6) * kAtomBytes + (r >> 3) * 1024 + (r & 7) * 128 + ((((c & 63) >> 3) ^ (r & 7)) << 4) + (c & 7) * 2;
-    *reinterpret_cast<T*>(smem + C::kOffBd + off) = v;
-  }
-  fence_proxy_async_smem();
   tc_fence_before();
-  __syncthreads();
+  __syncthreads();  // barriers and the tensor-memory base exist; the producer can start filling the X stages
   tc_fence_after();
   const uint32_t tmem = misc->tmem_base;
+
+  if (warp != 0) {
+    const int t13 = tid - 32;  // 0 .. 415 over warps 1-13
+    // R^T as a K-major operand: row = output column n, k runs along the row; 128-byte swizzle within 8-row groups
+    for (int idx = t13; idx < NDIM * NDIM; idx += kThreads - 32) {
+      const int j = idx / NDIM, n = idx % NDIM;  // R[j][n]
+      const uint32_t off = (j >> 6) * (NDIM * 128) + (n >> 3) * 1024 + (n & 7) * 128 + ((((j & 63) >> 3) ^ (n & 7)) << 4) + (j & 7) * 2;
+      *reinterpret_cast<T*>(smem + C::kOffR + off) = right[idx];
+    }
+    // blockdiag(L^T): entry (row r = (g, i), column c = (g, k)) is L[k][i]; everything off the diagonal blocks is 0
+    for (int idx = t13; idx < C::kBdBytes / 16; idx += kThreads - 32)
+      reinterpret_cast<uint4*>(smem + C::kOffBd)[idx] = make_uint4(0, 0, 0, 0);
+    asm volatile("bar.sync 1, %0;" ::"n"(kThreads - 32) : "memory");
+    for (int pair = warp - 1; pair < rows_tile; pair += 13) {  // one (token, k) pair per warp pass: a row of L
+      const int gg = pair / m, kk = pair - gg * m, c = gg * m + kk;
+      for (int i = lane; i < m; i += 32) {
+        const int r = gg * m + i;
+        const uint32_t off = (c >> 6) * kAtomBytes + (r >> 3) * 1024 + (r & 7) * 128 + ((((c & 63) >> 3) ^ (r & 7)) << 4) + (c & 7) * 2;
+        *reinterpret_cast<T*>(smem + C::kOffBd + off) = left[kk * m + i];
+      }
+    }
+    fence_proxy_async_smem();
+    asm volatile("bar.sync 1, %0;" ::"n"(kThreads - 32) : "memory");
+  }
 
   // ---- roles ---------------------------------------------------------------------------------------
   if (warp == 0) {
@@ -264,6 +337,7 @@ flatquant_sm100_kernel(const __grid_constant__ CUtensorMap x_map, const T* __res
     const int g = r / m, mi = r - g * m;
     const bool warp_uniform = (g_tokens == 1) || ((m & 31) == 0);
     const int feat = m * NDIM;
+    constexpr bool kHold = (NDIM == 64) && (MODE != kTransform);  // whole row stays in registers between the passes
     int it = 0;
     for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++it) {
       if ((it & 1) != e) continue;
@@ -274,15 +348,26 @@ flatquant_sm100_kernel(const __grid_constant__ CUtensorMap x_map, const T* __res
       const bool valid = r < rows_tile && tok < tokens;
       const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (2 + e) * NDIM;
 
+      uint32_t held[kHold ? 2 : 1][32];
       float amax = 0.f;
       if (MODE != kTransform) {
-#pragma unroll
-        for (int c0 = 0; c0 < NDIM; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(taddr + c0, v);
+        if (kHold) {
+          tmem_ld_32x32b_x32(taddr, held[0]);
+          tmem_ld_32x32b_x32(taddr + 32, held[kHold ? 1 : 0]);
           tmem_ld_wait();
+          tc_fence_before();
+          mbar_arrive(smem_u32(&misc->d2_empty[e]));  // accumulator stage is free again
 #pragma unroll
-          for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(__uint_as_float(v[i])));
+          for (int i = 0; i < 32; ++i)
+            amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(held[0][i])), fabsf(__uint_as_float(held[kHold ? 1 : 0][i]))));
+        } else {
+#pragma unroll
+          for (int c0 = 0; c0 < NDIM; c0 += 32) {
+            tmem_ld_32x32b_x32(taddr + c0, held[0]);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(__uint_as_float(held[0][i])));
+          }
         }
         if (!valid) amax = 0.f;
         amax = DT<T>::rnd(amax);  // max of the rounded values = rounded max
@@ -308,12 +393,15 @@ flatquant_sm100_kernel(const __grid_constant__ CUtensorMap x_map, const T* __res
         inv_s = __frcp_rn(s);
         if (valid && mi == 0) store_scale(scales, tok, s, scale_dtype);
       }
+      const bool zero_scale = (MODE != kTransform) && (s == 0.f);  // fp16 only: all-zero (or all-subnormal) row
 
 #pragma unroll
       for (int c0 = 0; c0 < NDIM; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(taddr + c0, v);
-        tmem_ld_wait();
+        uint32_t(&v)[32] = held[kHold ? (c0 >> 5) : 0];
+        if (!kHold) {
+          tmem_ld_32x32b_x32(taddr + c0, v);
+          tmem_ld_wait();
+        }
         if (MODE == kTransform) {
           if (valid) {
             float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + tok * feat + mi * NDIM + c0);
@@ -322,46 +410,40 @@ flatquant_sm100_kernel(const __grid_constant__ CUtensorMap x_map, const T* __res
               dst[j] = make_float4(DT<T>::rnd(__uint_as_float(v[4 * j])), DT<T>::rnd(__uint_as_float(v[4 * j + 1])),
                                    DT<T>::rnd(__uint_as_float(v[4 * j + 2])), DT<T>::rnd(__uint_as_float(v[4 * j + 3])));
           }
-        } else if (MODE == kPacked) {
-          uint32_t w[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint32_t acc = 0;
-#pragma unroll
-            for (int i = 7; i >= 0; --i) {
-              const float z = DT<T>::rnd(__uint_as_float(v[8 * j + i]));
-              const float qv = fminf(fmaxf(quotient<T>(z, s, inv_s), -8.f), 7.f);
-              // adding 1.5 * 2^23 + 8 leaves rint(q) + 8 (round half even) in the low mantissa bits
-              acc = acc * 16u + __float_as_uint(qv + 12582920.0f);
-            }
-            w[j] = acc - 0x3F400000u;  // the eight float exponent patterns, shifted and summed mod 2^32
-          }
-          if (valid) {
-            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(out) + tok * (feat / 8) + (mi * NDIM + c0) / 8);
-            *dst = make_uint4(w[0], w[1], w[2], w[3]);
-          }
         } else {
-          uint32_t w[8];
+          uint32_t pb[4], qb[4];  // nibble-bytes of the 32 elements, 4 + 4 per group of 8
+          if (!zero_scale) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            uint32_t word = 0;
+            for (int j = 0; j < 4; ++j) nibble_bytes<T>(v, 8 * j, s, inv_s, pb[j], qb[j]);
+          } else {
+            // the reference divides by zero here: +-inf clamps to 7 / -8, 0/0 counts as 0
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float z = DT<T>::rnd(__uint_as_float(v[4 * j + i]));
-              const float qv = fminf(fmaxf(quotient<T>(z, s, inv_s), -8.f), 7.f);
-              word |= (__float_as_uint(qv + 12582912.0f) & 0xFFu) << (8 * i);  // low byte = two's complement code
+            for (int j = 0; j < 4; ++j) {
+              pb[j] = qb[j] = 0;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float z0 = DT<T>::rnd(__uint_as_float(v[8 * j + i])), z1 = DT<T>::rnd(__uint_as_float(v[8 * j + 4 + i]));
+                pb[j] |= (uint32_t)(z0 > 0.f ? 15 : (z0 < 0.f ? 0 : 8)) << (8 * i);
+                qb[j] |= (uint32_t)(z1 > 0.f ? 15 : (z1 < 0.f ? 0 : 8)) << (8 * i);
+              }
             }
-            w[j] = word;
           }
-          if (valid) {
+          if (MODE == kPacked) {
+            if (valid) {
+              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(out) + tok * (feat / 8) + (mi * NDIM + c0) / 8);
+              *dst = make_uint4(pack8(pb[0], qb[0]), pack8(pb[1], qb[1]), pack8(pb[2], qb[2]), pack8(pb[3], qb[3]));
+            }
+          } else if (valid) {
             uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<int8_t*>(out) + tok * feat + mi * NDIM + c0);
-            dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-            dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            dst[0] = make_uint4(bytes4(pb[0]), bytes4(qb[0]), bytes4(pb[1]), bytes4(qb[1]));
+            dst[1] = make_uint4(bytes4(pb[2]), bytes4(qb[2]), bytes4(pb[3]), bytes4(qb[3]));
           }
         }
       }
-      tc_fence_before();
-      mbar_arrive(smem_u32(&misc->d2_empty[e]));
+      if (!kHold) {
+        tc_fence_before();
+        mbar_arrive(smem_u32(&misc->d2_empty[e]));
+      }
     }
   }
 
