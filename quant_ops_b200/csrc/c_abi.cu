@@ -153,7 +153,7 @@ int qo_flatquant_quantize(const void* x, int64_t ldx, const void* left, const vo
   if (tokens == 0) return QO_OK;
   if ((rc = require_device(nullptr))) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const bool fast_ok = flatquant_sm100_supported(ldx, m, n, in_dtype, x, clip_ratio);
+  const bool fast_ok = flatquant_sm100_supported(ldx, m, n, in_dtype, x, left, right, clip_ratio);
   if (t_policy == 2 && !fast_ok)
     return fail(QO_ERR_UNSUPPORTED, "flatquant: no tcgen05 kernel for m=%d n=%d dtype=%d ldx=%lld", m, n, in_dtype, (long long)ldx);
   if (fast_ok && t_policy != 1) {
@@ -174,7 +174,7 @@ int qo_flatquant_transform(const void* x, int64_t ldx, const void* left, const v
   if (tokens == 0) return QO_OK;
   if ((rc = require_device(nullptr))) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const bool fast_ok = flatquant_sm100_supported(ldx, m, n, in_dtype, x, 1.0f);
+  const bool fast_ok = flatquant_sm100_supported(ldx, m, n, in_dtype, x, left, right, 1.0f);
   if (t_policy == 2 && !fast_ok)
     return fail(QO_ERR_UNSUPPORTED, "flatquant_transform: no tcgen05 kernel for m=%d n=%d dtype=%d", m, n, in_dtype);
   if (fast_ok && t_policy != 1) {

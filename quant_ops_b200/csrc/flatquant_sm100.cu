@@ -24,18 +24,16 @@
 #include <cstdlib>
 #include <mutex>
 
-#include "qo_internal.cuh"
-#include "sm100_ptx.cuh"
+#include "flatquant_sm100_common.cuh"
 
 namespace qo {
 namespace {
 
 using namespace ptx;
+using namespace fq;
 
 constexpr int kThreads = 448;  // 14 warps
-constexpr int kAtomBytes = 128 * 128;  // 128 rows of one 128-byte swizzle atom
 
-enum Mode { kInt8 = 0, kPacked = 1, kTransform = 2 };
 
 template <int NDIM>
 struct Cfg {
@@ -51,7 +49,7 @@ struct Cfg {
   static constexpr int kOffBd = kOffR + kRBytes;
   static constexpr int kOffMisc = kOffBd + kBdBytes;
   static constexpr int kSmemBytes = kOffMisc + 1024 /*barriers, absmax slots*/ + 1024 /*alignment slack*/;
-  static constexpr int kTmemCols = 4 * NDIM;              // two stages each of Y and Z accumulators
+  static constexpr int kTmemCols = 512;                   // two stages each of Y and Z accumulators (+ blockdiag(L^T) for N = 64)
 };
 
 struct Misc {
@@ -63,99 +61,6 @@ struct Misc {
   int absmax_bits[2][3][8];
 };
 
-template <typename T> struct Fmt;
-template <> struct Fmt<__half> { static constexpr uint32_t id = 0; };
-template <> struct Fmt<__nv_bfloat16> { static constexpr uint32_t id = 1; };
-
-template <typename T>
-__device__ __forceinline__ uint32_t pack2(float a, float b);
-template <>
-__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
-  __half2 h = __floats2half2_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
-template <>
-__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
-
-// Two-wide arithmetic in the activation dtype, used by the quantize pass.  Everything here runs on the ALU / FMA
-// pipes (packed converts, packed min / max / add); none of it touches the conversion unit.
-//   cvt(lo, hi)      two float32 -> packed pair, round to nearest even
-//   lo(p), hi(p)     packed pair -> float32
-//   nibbles(q)       clamp both halves to [-8, 7], then add the constant whose spacing is 1 (200 for bf16, 1032 for
-//                    fp16): the sum is rint(q) + 8 with ties to even, and it sits in the low 4 bits of each half
-//   quot(z0, z1)     round(z / s) for both; bf16 multiplies by 1/s (exact, see the file comment), fp16 refines the
-//                    product with two FMAs, which gives the correctly rounded quotient (Markstein)
-template <typename T> struct P2;
-template <> struct P2<__nv_bfloat16> {
-  static constexpr uint32_t kByteMask = 0x0F0F0F0Fu;  // the nibble's byte also carries exponent bits
-  static __device__ __forceinline__ uint32_t cvt(float lo, float hi) {
-    uint32_t d;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
-    return d;
-  }
-  static __device__ __forceinline__ float lo(uint32_t p) { return __uint_as_float(p << 16); }
-  static __device__ __forceinline__ float hi(uint32_t p) { return __uint_as_float(p & 0xFFFF0000u); }
-  static __device__ __forceinline__ uint32_t nibbles(uint32_t q) {
-    uint32_t d;
-    asm("{\n\t.reg .b32 t;\n\t"
-        "max.bf16x2 t, %1, %2;\n\t"
-        "min.bf16x2 t, t, %3;\n\t"
-        "add.rn.bf16x2 %0, t, %4;\n\t}"
-        : "=r"(d) : "r"(q), "r"(0xC100C100u), "r"(0x40E040E0u), "r"(0x43484348u));
-    return d;
-  }
-  static __device__ __forceinline__ uint32_t quot(float z0, float z1, float, float inv_s) { return cvt(z0 * inv_s, z1 * inv_s); }
-};
-template <> struct P2<__half> {
-  static constexpr uint32_t kByteMask = 0xFFFFFFFFu;
-  static __device__ __forceinline__ uint32_t cvt(float lo, float hi) {
-    uint32_t d;
-    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
-    return d;
-  }
-  static __device__ __forceinline__ float lo(uint32_t p) { return __low2float(*reinterpret_cast<__half2*>(&p)); }
-  static __device__ __forceinline__ float hi(uint32_t p) { return __high2float(*reinterpret_cast<__half2*>(&p)); }
-  static __device__ __forceinline__ uint32_t nibbles(uint32_t q) {
-    uint32_t d;
-    asm("{\n\t.reg .b32 t;\n\t"
-        "max.f16x2 t, %1, %2;\n\t"
-        "min.f16x2 t, t, %3;\n\t"
-        "add.rn.f16x2 %0, t, %4;\n\t}"
-        : "=r"(d) : "r"(q), "r"(0xC800C800u), "r"(0x47004700u), "r"(0x64086408u));
-    return d;
-  }
-  static __device__ __forceinline__ uint32_t quot(float z0, float z1, float s, float inv_s) {
-    float q0 = z0 * inv_s, q1 = z1 * inv_s;
-    q0 = fmaf(fmaf(-q0, s, z0), inv_s, q0);
-    q1 = fmaf(fmaf(-q1, s, z1), inv_s, q1);
-    return cvt(q0, q1);
-  }
-};
-
-// 32 accumulator values of one row -> 32 offset-binary nibbles, as 4 words of 4 bytes-with-a-nibble each pair
-// (P = elements 0..3, Q = elements 4..7 of a group of 8; see pack8 / bytes4)
-template <typename T>
-__device__ __forceinline__ void nibble_bytes(const uint32_t (&v)[32], int base, float s, float inv_s, uint32_t& p, uint32_t& q) {
-  uint32_t t[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint32_t zz = P2<T>::cvt(__uint_as_float(v[base + 2 * i]), __uint_as_float(v[base + 2 * i + 1]));  // round z
-    t[i] = P2<T>::nibbles(P2<T>::quot(P2<T>::lo(zz), P2<T>::hi(zz), s, inv_s));
-  }
-  p = __byte_perm(t[0], t[1], 0x6420) & P2<T>::kByteMask;  // bytes: elements 0, 1, 2, 3
-  q = __byte_perm(t[2], t[3], 0x6420) & P2<T>::kByteMask;  // bytes: elements 4, 5, 6, 7
-}
-// 8 nibble-bytes -> one packed word, nibble i at bits 4i
-__device__ __forceinline__ uint32_t pack8(uint32_t p, uint32_t q) {
-  p |= p >> 4;
-  q |= q >> 4;
-  return __byte_perm(p, q, 0x6420);
-}
-// 4 nibble-bytes (offset binary) -> 4 signed bytes
-__device__ __forceinline__ uint32_t bytes4(uint32_t p) { return ((p | 0x80808080u) - 0x08080808u) ^ 0x80808080u; }
 
 __device__ __forceinline__ void report(uint32_t* status, Misc* misc, uint32_t code) {
   atomicCAS(status, 0u, code);
@@ -206,28 +111,88 @@ flatquant_sm100_kernel(const __grid_constant__ CUtensorMap x_map, const T* __res
   tc_fence_after();
   const uint32_t tmem = misc->tmem_base;
 
+  // blockdiag(L^T) lives in tensor memory when there is room beside the accumulators (N = 64), else in shared memory
+  constexpr bool kBdInTmem = (NDIM == 64);
+  const uint32_t tmem_bd = tmem + 4 * NDIM;
+
   if (warp != 0) {
-    const int t13 = tid - 32;  // 0 .. 415 over warps 1-13
-    // R^T as a K-major operand: row = output column n, k runs along the row; 128-byte swizzle within 8-row groups
-    for (int idx = t13; idx < NDIM * NDIM; idx += kThreads - 32) {
-      const int j = idx / NDIM, n = idx % NDIM;  // R[j][n]
-      const uint32_t off = (j >> 6) * (NDIM * 128) + (n >> 3) * 1024 + (n & 7) * 128 + ((((j & 63) >> 3) ^ (n & 7)) << 4) + (j & 7) * 2;
-      *reinterpret_cast<T*>(smem + C::kOffR + off) = right[idx];
+    constexpr int kStagers = kThreads - 32;  // warps 1-13
+    const int t13 = tid - 32;
+    // Step 1: raw copies of L and R into shared memory that nothing uses yet, 16-byte loads all in flight at once.
+    T* raw_l = reinterpret_cast<T*>(smem + (kBdInTmem ? C::kOffBd : C::kOffY));
+    T* raw_r = reinterpret_cast<T*>(smem + (kBdInTmem ? C::kOffY : C::kOffY + C::kYStageBytes));
+    {
+      const int l_chunks = (m * m) / 8, r_chunks = NDIM * NDIM / 8;
+      constexpr int kMaxIter = (2 * 128 * 128 / 8 + kStagers - 1) / kStagers;
+      uint4 tmp[kMaxIter];
+#pragma unroll
+      for (int i = 0; i < kMaxIter; ++i) {
+        const int c = t13 + i * kStagers;
+        if (c < l_chunks) tmp[i] = reinterpret_cast<const uint4*>(left)[c];
+        else if (c - l_chunks < r_chunks) tmp[i] = reinterpret_cast<const uint4*>(right)[c - l_chunks];
+      }
+#pragma unroll
+      for (int i = 0; i < kMaxIter; ++i) {
+        const int c = t13 + i * kStagers;
+        if (c < l_chunks) reinterpret_cast<uint4*>(raw_l)[c] = tmp[i];
+        else if (c - l_chunks < r_chunks) reinterpret_cast<uint4*>(raw_r)[c - l_chunks] = tmp[i];
+      }
+      for (int i = l_chunks * 8 + t13; i < m * m; i += kStagers) raw_l[i] = left[i];  // tail when m*m is not a multiple of 8
+      if (!kBdInTmem)
+        for (int idx = t13; idx < C::kBdBytes / 16; idx += kStagers) reinterpret_cast<uint4*>(smem + C::kOffBd)[idx] = make_uint4(0, 0, 0, 0);
     }
-    // blockdiag(L^T): entry (row r = (g, i), column c = (g, k)) is L[k][i]; everything off the diagonal blocks is 0
-    for (int idx = t13; idx < C::kBdBytes / 16; idx += kThreads - 32)
-      reinterpret_cast<uint4*>(smem + C::kOffBd)[idx] = make_uint4(0, 0, 0, 0);
-    asm volatile("bar.sync 1, %0;" ::"n"(kThreads - 32) : "memory");
-    for (int pair = warp - 1; pair < rows_tile; pair += 13) {  // one (token, k) pair per warp pass: a row of L
-      const int gg = pair / m, kk = pair - gg * m, c = gg * m + kk;
-      for (int i = lane; i < m; i += 32) {
-        const int r = gg * m + i;
-        const uint32_t off = (c >> 6) * kAtomBytes + (r >> 3) * 1024 + (r & 7) * 128 + ((((c & 63) >> 3) ^ (r & 7)) << 4) + (c & 7) * 2;
-        *reinterpret_cast<T*>(smem + C::kOffBd + off) = left[kk * m + i];
+    asm volatile("bar.sync 1, %0;" ::"n"(kStagers) : "memory");
+
+    // Step 2: operands in the layouts the MMAs read.
+    if (kBdInTmem && warp >= 2 && warp < 6) {
+      // lane r of tensor memory = row r of blockdiag(L^T); 32-bit column j holds k = 2j (low half) and 2j + 1
+      const int q = warp & 3, r = q * 32 + lane;
+      const int gg = r / m, i = r - gg * m, c_lo = gg * m;
+      const bool row_ok = r < rows_tile;
+      const uint16_t* rl = reinterpret_cast<const uint16_t*>(raw_l);
+#pragma unroll
+      for (int cb = 0; cb < 64; cb += 8) {
+        uint32_t w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int k0 = 2 * (cb + j) - c_lo, k1 = k0 + 1;
+          const uint32_t v0 = (row_ok && k0 >= 0 && k0 < m) ? rl[k0 * m + i] : 0u;
+          const uint32_t v1 = (row_ok && k1 >= 0 && k1 < m) ? rl[k1 * m + i] : 0u;
+          w[j] = v0 | (v1 << 16);
+        }
+        tmem_st_32x32b_x8(tmem_bd + ((uint32_t)(q * 32) << 16) + cb, w);
+      }
+      tmem_st_wait();
+    } else {
+      // R^T as a K-major operand: row = output column n, k = j runs along the row, 128-byte swizzle per 8 rows
+      const int first = kBdInTmem ? (warp == 1 ? lane : (warp - 5) * 32 + lane) : t13;  // dense index over the warps here
+      constexpr int kWorkers = kBdInTmem ? kStagers - 128 : kStagers;
+      for (int c = first; c < NDIM * NDIM / 8; c += kWorkers) {
+        const int j = c / (NDIM / 8), n0 = (c % (NDIM / 8)) * 8;  // R[j][n0 .. n0+7]
+        const uint4 v = reinterpret_cast<const uint4*>(raw_r)[c];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e8 = 0; e8 < 8; ++e8) {
+          const int n = n0 + e8;
+          const uint32_t off = (j >> 6) * (NDIM * 128) + (n >> 3) * 1024 + (n & 7) * 128 + ((((j & 63) >> 3) ^ (n & 7)) << 4) + (j & 7) * 2;
+          *reinterpret_cast<uint16_t*>(smem + C::kOffR + off) = (uint16_t)(w[e8 >> 1] >> (16 * (e8 & 1)));
+        }
+      }
+      if (!kBdInTmem) {
+        // diagonal blocks of blockdiag(L^T) in shared memory: entry (row (g, i), column (g, k)) = L[k][i]
+        const uint16_t* rl = reinterpret_cast<const uint16_t*>(raw_l);
+        for (int idx = t13; idx < rows_tile * m; idx += kStagers) {
+          const int gk = idx / m, i = idx - gk * m;  // gk = g * m + k = the column
+          const int gg = gk / m, r = gg * m + i, c = gk;
+          const uint32_t off = (c >> 6) * kAtomBytes + (r >> 3) * 1024 + (r & 7) * 128 + ((((c & 63) >> 3) ^ (r & 7)) << 4) + (c & 7) * 2;
+          *reinterpret_cast<uint16_t*>(smem + C::kOffBd + off) = rl[(gk - gg * m) * m + i];
+        }
       }
     }
     fence_proxy_async_smem();
-    asm volatile("bar.sync 1, %0;" ::"n"(kThreads - 32) : "memory");
+    tc_fence_before();
+    asm volatile("bar.sync 1, %0;" ::"n"(kStagers) : "memory");
+    tc_fence_after();
   }
 
   // ---- roles ---------------------------------------------------------------------------------------
@@ -279,9 +244,13 @@ flatquant_sm100_kernel(const __grid_constant__ CUtensorMap x_map, const T* __res
         tc_fence_after();
         const uint32_t a_base = smem_base + C::kOffBd, b_base = smem_base + C::kOffY + s * C::kYStageBytes;
         for (int ks = 0; ks < k2 / 16; ++ks) {
-          const uint64_t ad = umma_smem_desc_sw128(a_base + (ks >> 2) * kAtomBytes + (ks & 3) * 32, 16, 1024);
           const uint64_t bd = umma_smem_desc_sw128(b_base + ks * 2048, y_lbo, y_sbo);
-          mma_f16_ss(tmem + (2 + s) * NDIM, ad, bd, idesc2, ks > 0);
+          if (kBdInTmem) {
+            mma_f16_ts(tmem + (2 + s) * NDIM, tmem_bd + ks * 8, bd, idesc2, ks > 0);  // 16 k = 8 packed columns
+          } else {
+            const uint64_t ad = umma_smem_desc_sw128(a_base + (ks >> 2) * kAtomBytes + (ks & 3) * 32, 16, 1024);
+            mma_f16_ss(tmem + (2 + s) * NDIM, ad, bd, idesc2, ks > 0);
+          }
         }
         mma_commit(smem_u32(&misc->y_empty[s]));
         mma_commit(smem_u32(&misc->d2_full[s]));
@@ -527,13 +496,14 @@ int launch_mode(int mode, const CUtensorMap& map, const void* left, const void* 
 
 uint32_t* device_status_word(int dev) { return status_word(dev); }
 
-bool flatquant_sm100_supported(int64_t ldx, int m, int n, int in_dtype, const void* x, float clip) {
+bool flatquant_sm100_supported(int64_t ldx, int m, int n, int in_dtype, const void* x, const void* left, const void* right,
+                               float clip) {
   if (in_dtype != QO_F16 && in_dtype != QO_BF16) return false;
   if (!(clip > 0.f)) return false;                            // the single running absmax needs a positive clip ratio
   if (n != 64 && n != 128) return false;
   if (m < 16 || m > 128) return false;
   if (ldx % 8) return false;                                  // TMA: row stride must be a multiple of 16 bytes
-  if (reinterpret_cast<uintptr_t>(x) % 16) return false;
+  if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(left) % 16 || reinterpret_cast<uintptr_t>(right) % 16) return false;
   return encode_fn() != nullptr;
 }
 
@@ -551,7 +521,8 @@ int launch_flatquant_sm100_mode(int mode, const void* x, int64_t ldx, const void
   CUtensorMap map;
   const cuuint64_t dims[3] = {(cuuint64_t)n, (cuuint64_t)m, (cuuint64_t)tokens};
   const cuuint64_t strides[2] = {(cuuint64_t)n * 2, (cuuint64_t)ldx * 2};
-  const cuuint32_t box[3] = {64, (cuuint32_t)m, (cuuint32_t)(128 / m)};
+  const bool batched = flatquant_sm100_n64_supported(m, n);  // groups of 4 tokens, wide second product
+  const cuuint32_t box[3] = {64, (cuuint32_t)m, (cuuint32_t)(batched ? 4 : 128 / m)};
   const cuuint32_t estr[3] = {1, 1, 1};
   const CUresult r = encode_fn()(&map, in_dtype == QO_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
                                  3, const_cast<void*>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -559,6 +530,8 @@ int launch_flatquant_sm100_mode(int mode, const void* x, int64_t ldx, const void
                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(QO_ERR_CUDA, "flatquant: cuTensorMapEncodeTiled failed with code %d", (int)r);
 
+  if (batched)
+    return launch_flatquant_sm100_n64(mode, &map, left, right, codes, scales, tokens, m, clip, in_dtype, scale_dtype, status, stream);
   if (in_dtype == QO_BF16) {
     if (n == 64) return launch_mode<__nv_bfloat16, 64>(mode, map, left, right, codes, scales, tokens, m, clip, scale_dtype, status, stream);
     return launch_mode<__nv_bfloat16, 128>(mode, map, left, right, codes, scales, tokens, m, clip, scale_dtype, status, stream);

@@ -1,0 +1,116 @@
+// Device helpers shared by the tcgen05 quantizer kernels: operand formats, two-wide arithmetic in the activation
+// dtype, nibble packing.
+#pragma once
+
+#include "qo_internal.cuh"
+#include "sm100_ptx.cuh"
+
+namespace qo {
+namespace fq {
+
+constexpr int kAtomBytes = 128 * 128;  // 128 rows of one 128-byte swizzle atom
+enum Mode { kInt8 = 0, kPacked = 1, kTransform = 2 };
+
+template <typename T> struct Fmt;
+template <> struct Fmt<__half> { static constexpr uint32_t id = 0; };
+template <> struct Fmt<__nv_bfloat16> { static constexpr uint32_t id = 1; };
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Two-wide arithmetic in the activation dtype, used by the quantize pass.  Everything here runs on the ALU / FMA
+// pipes (packed converts, packed min / max / add); none of it touches the conversion unit.
+//   cvt(lo, hi)      two float32 -> packed pair, round to nearest even
+//   lo(p), hi(p)     packed pair -> float32
+//   nibbles(q)       clamp both halves to [-8, 7], then add the constant whose spacing is 1 (200 for bf16, 1032 for
+//                    fp16): the sum is rint(q) + 8 with ties to even, and it sits in the low 4 bits of each half
+//   quot(z0, z1)     round(z / s) for both; bf16 multiplies by 1/s (exact, see the file comment), fp16 refines the
+//                    product with two FMAs, which gives the correctly rounded quotient (Markstein)
+template <typename T> struct P2;
+template <> struct P2<__nv_bfloat16> {
+  static constexpr uint32_t kByteMask = 0x0F0F0F0Fu;  // the nibble's byte also carries exponent bits
+  static __device__ __forceinline__ uint32_t cvt(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+  }
+  static __device__ __forceinline__ float lo(uint32_t p) { return __uint_as_float(p << 16); }
+  static __device__ __forceinline__ float hi(uint32_t p) { return __uint_as_float(p & 0xFFFF0000u); }
+  static __device__ __forceinline__ uint32_t nibbles(uint32_t q) {
+    uint32_t d;
+    asm("{\n\t.reg .b32 t;\n\t"
+        "max.bf16x2 t, %1, %2;\n\t"
+        "min.bf16x2 t, t, %3;\n\t"
+        "add.rn.bf16x2 %0, t, %4;\n\t}"
+        : "=r"(d) : "r"(q), "r"(0xC100C100u), "r"(0x40E040E0u), "r"(0x43484348u));
+    return d;
+  }
+  static __device__ __forceinline__ uint32_t quot(float z0, float z1, float, float inv_s) { return cvt(z0 * inv_s, z1 * inv_s); }
+};
+template <> struct P2<__half> {
+  static constexpr uint32_t kByteMask = 0xFFFFFFFFu;
+  static __device__ __forceinline__ uint32_t cvt(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+  }
+  static __device__ __forceinline__ float lo(uint32_t p) { return __low2float(*reinterpret_cast<__half2*>(&p)); }
+  static __device__ __forceinline__ float hi(uint32_t p) { return __high2float(*reinterpret_cast<__half2*>(&p)); }
+  static __device__ __forceinline__ uint32_t nibbles(uint32_t q) {
+    uint32_t d;
+    asm("{\n\t.reg .b32 t;\n\t"
+        "max.f16x2 t, %1, %2;\n\t"
+        "min.f16x2 t, t, %3;\n\t"
+        "add.rn.f16x2 %0, t, %4;\n\t}"
+        : "=r"(d) : "r"(q), "r"(0xC800C800u), "r"(0x47004700u), "r"(0x64086408u));
+    return d;
+  }
+  static __device__ __forceinline__ uint32_t quot(float z0, float z1, float s, float inv_s) {
+    float q0 = z0 * inv_s, q1 = z1 * inv_s;
+    q0 = fmaf(fmaf(-q0, s, z0), inv_s, q0);
+    q1 = fmaf(fmaf(-q1, s, z1), inv_s, q1);
+    return cvt(q0, q1);
+  }
+};
+
+// 32 accumulator values of one row -> 32 offset-binary nibbles, as 4 words of 4 bytes-with-a-nibble each pair
+// (P = elements 0..3, Q = elements 4..7 of a group of 8; see pack8 / bytes4)
+template <typename T>
+__device__ __forceinline__ void nibble_bytes(const uint32_t (&v)[32], int base, float s, float inv_s, uint32_t& p, uint32_t& q) {
+  uint32_t t[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t zz = P2<T>::cvt(__uint_as_float(v[base + 2 * i]), __uint_as_float(v[base + 2 * i + 1]));  // round z
+    t[i] = P2<T>::nibbles(P2<T>::quot(P2<T>::lo(zz), P2<T>::hi(zz), s, inv_s));
+  }
+  p = __byte_perm(t[0], t[1], 0x6420) & P2<T>::kByteMask;  // bytes: elements 0, 1, 2, 3
+  q = __byte_perm(t[2], t[3], 0x6420) & P2<T>::kByteMask;  // bytes: elements 4, 5, 6, 7
+}
+// 8 nibble-bytes -> one packed word, nibble i at bits 4i
+__device__ __forceinline__ uint32_t pack8(uint32_t p, uint32_t q) {
+  p |= p >> 4;
+  q |= q >> 4;
+  return __byte_perm(p, q, 0x6420);
+}
+// 4 nibble-bytes (offset binary) -> 4 signed bytes
+__device__ __forceinline__ uint32_t bytes4(uint32_t p) { return ((p | 0x80808080u) - 0x08080808u) ^ 0x80808080u; }
+
+}  // namespace fq
+
+// one launch of the batched N = 64 kernel (flatquant_sm100_n64.cu); same contract as launch_flatquant_sm100_mode
+bool flatquant_sm100_n64_supported(int m, int n);
+int launch_flatquant_sm100_n64(int mode, const void* x_map, const void* left, const void* right, void* out, void* scales,
+                               int64_t tokens, int m, float clip, int in_dtype, int scale_dtype, uint32_t* status,
+                               cudaStream_t stream);
+
+}  // namespace qo

@@ -1,0 +1,371 @@
+// FlatQuant quantizer for sm_100a, right transform of size 64 (features = M x 64 with M in {16, 32, 48, 64}):
+// the activation-scale configuration (4096 = 64 x 64) runs here.
+//
+// A tcgen05.mma costs about the same for N = 64 as for N = 256, so the work is shaped into few, wide instructions.
+// One persistent CTA per SM works on groups of 4 tokens:
+//
+//   warp 0      TMA: 3-D tensor map (n, m, token), box 64 x M x 4 -> 4M rows of 128 bytes, 128-byte swizzle
+//   warp 1      MMA issuer
+//                 Y  = X . R      per 128-row slice of the group: A = X rows (K-major), B = R^T (K-major), N = 64
+//                 Z  = LL . Y4    once per group: A = LL = floor(128/M) copies of L^T stacked (K-major),
+//                                 B = the 4 tokens' Y side by side along N (N-major, N = 256), K = M
+//   warps 2-5   Y pass: tensor memory -> round to the activation dtype -> shared memory in the B layout
+//   warps 6-13  quantize pass: lane block c of group e owns token e*copies + c of the group; thread = one row of that
+//               token: absmax (shared-memory atomics per token), scale, int4 codes, 16-byte stores
+//
+// Stacking copies of L^T makes every copy's lanes hold the same Z rows, so different lane blocks can serve
+// different tokens and all 256 quantize threads have work.  No block-diagonal padding is multiplied.
+//
+// Rounding points and the exactness arguments are those of flatquant_sm100.cu (reference:
+// src/quant_ops/ops/quantization/flatquant/ops.py:99-117).  Every mbarrier wait is bounded.
+#include "flatquant_sm100_common.cuh"
+
+namespace qo {
+namespace {
+
+using namespace ptx;
+using namespace fq;
+
+constexpr int kThreads = 448;
+constexpr int kGroup = 4;                      // tokens per group
+constexpr int kXStages = 3;
+constexpr int kStageBytes = 256 * 128;         // up to 4 x 64 rows of 128 bytes
+constexpr int kOffX = 0;
+constexpr int kOffY = kOffX + kXStages * kStageBytes;
+constexpr int kOffR = kOffY + 2 * kStageBytes;
+constexpr int kOffLL = kOffR + 64 * 128;
+constexpr int kOffMisc = kOffLL + kAtomBytes;
+constexpr int kSmemBytes = kOffMisc + 1024 + 1024;
+constexpr int kTmemCols = 512;                 // Y accumulators: 2 stages x 128 columns; Z accumulators: 256 columns
+constexpr int kColZ = 256;
+
+struct Misc {
+  uint64_t full_x[kXStages], empty_x[kXStages];
+  uint64_t d1_full[2], d1_empty[2], y_full[2], y_empty[2], d2_full, d2_empty, group_sync[2];
+  uint32_t tmem_base;
+  int absmax_bits[2][3][8];
+};
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restrict__ left, const T* __restrict__ right,
+                     void* __restrict__ out, void* __restrict__ scales, long long tokens, int m, float clip,
+                     int scale_dtype, uint32_t* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Misc* misc = reinterpret_cast<Misc*>(smem + kOffMisc);
+  const uint32_t smem_base = smem_u32(smem);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int copies = 128 / m;                 // copies of L^T stacked in the A operand of the second product
+  const int rows_group = kGroup * m;          // X / Y rows per group
+  const int slices = (rows_group + 127) >> 7; // 128-row slices of the first product
+  const long long ngroups = (tokens + kGroup - 1) / kGroup;
+
+  if (tid == 0) {
+    for (int i = 0; i < kXStages; ++i) { mbar_init(smem_u32(&misc->full_x[i]), 1); mbar_init(smem_u32(&misc->empty_x[i]), 1); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&misc->d1_full[i]), 1);
+      mbar_init(smem_u32(&misc->d1_empty[i]), 128);
+      mbar_init(smem_u32(&misc->y_full[i]), 128);
+      mbar_init(smem_u32(&misc->y_empty[i]), 1);
+      mbar_init(smem_u32(&misc->group_sync[i]), 128);
+    }
+    mbar_init(smem_u32(&misc->d2_full), 1);
+    mbar_init(smem_u32(&misc->d2_empty), 256);
+    for (int i = 0; i < 2 * 3 * 8; ++i) (&misc->absmax_bits[0][0][0])[i] = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&x_map);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&misc->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();  // barriers and the tensor-memory base exist; the producer starts filling the X stages
+  tc_fence_after();
+  const uint32_t tmem = misc->tmem_base;
+
+  if (warp != 0) {
+    constexpr int kStagers = kThreads - 32;
+    const int t13 = tid - 32;
+    // raw copies of L and R into the (still unused) Y stages, all 16-byte loads in flight at once
+    uint16_t* raw_l = reinterpret_cast<uint16_t*>(smem + kOffY);
+    uint16_t* raw_r = reinterpret_cast<uint16_t*>(smem + kOffY + kStageBytes);
+    {
+      const int l_chunks = (m * m) / 8, r_chunks = 64 * 64 / 8;
+      constexpr int kMaxIter = (2 * 64 * 64 / 8 + kStagers - 1) / kStagers;
+      uint4 tmp[kMaxIter];
+#pragma unroll
+      for (int i = 0; i < kMaxIter; ++i) {
+        const int c = t13 + i * kStagers;
+        if (c < l_chunks) tmp[i] = reinterpret_cast<const uint4*>(left)[c];
+        else if (c - l_chunks < r_chunks) tmp[i] = reinterpret_cast<const uint4*>(right)[c - l_chunks];
+      }
+#pragma unroll
+      for (int i = 0; i < kMaxIter; ++i) {
+        const int c = t13 + i * kStagers;
+        if (c < l_chunks) reinterpret_cast<uint4*>(raw_l)[c] = tmp[i];
+        else if (c - l_chunks < r_chunks) reinterpret_cast<uint4*>(raw_r)[c - l_chunks] = tmp[i];
+      }
+      for (int idx = t13; idx < kAtomBytes / 16; idx += kStagers) reinterpret_cast<uint4*>(smem + kOffLL)[idx] = make_uint4(0, 0, 0, 0);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kStagers) : "memory");
+    // R^T, K-major: row = output column n, k = j along the row
+    for (int c = t13; c < 64 * 64 / 8; c += kStagers) {
+      const int j = c >> 3, n0 = (c & 7) * 8;
+      const uint4 v = reinterpret_cast<const uint4*>(raw_r)[c];
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int e8 = 0; e8 < 8; ++e8) {
+        const int n = n0 + e8;
+        const uint32_t off = (n >> 3) * 1024 + (n & 7) * 128 + (((j >> 3) ^ (n & 7)) << 4) + (j & 7) * 2;
+        *reinterpret_cast<uint16_t*>(smem + kOffR + off) = (uint16_t)(w[e8 >> 1] >> (16 * (e8 & 1)));
+      }
+    }
+    // LL, K-major: row (copy, i), column k holds L[k][i]
+    const int ll_rows = copies * m;
+    for (int idx = t13; idx < ll_rows * m; idx += kStagers) {
+      const int k = idx / ll_rows, r = idx - k * ll_rows;
+      int i = r;
+      while (i >= m) i -= m;
+      const uint32_t off = (r >> 3) * 1024 + (r & 7) * 128 + (((k >> 3) ^ (r & 7)) << 4) + (k & 7) * 2;
+      *reinterpret_cast<uint16_t*>(smem + kOffLL + off) = raw_l[k * m + i];
+    }
+    fence_proxy_async_smem();
+    asm volatile("bar.sync 1, %0;" ::"n"(kStagers) : "memory");
+  }
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint32_t bytes = (uint32_t)(rows_group * 128);
+      int it = 0;
+      for (long long grp = blockIdx.x; grp < ngroups; grp += gridDim.x, ++it) {
+        const int s = it % kXStages, ph = (it / kXStages) & 1;
+        if (!mbar_wait(smem_u32(&misc->empty_x[s]), ph ^ 1)) { atomicCAS(status, 0u, 0x600u + s); break; }
+        const uint32_t bar = smem_u32(&misc->full_x[s]);
+        mbar_arrive_expect_tx(bar, bytes);
+        tma_load_3d(smem_base + kOffX + s * kStageBytes, &x_map, bar, 0, 0, (int)(grp * kGroup));
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc1 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 0, 0, 128, 64);
+      const uint32_t idesc2 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 0, 1, 128, 256);
+      long long mine = 0;
+      if ((long long)blockIdx.x < ngroups) mine = (ngroups - blockIdx.x + gridDim.x - 1) / gridDim.x;
+      bool ok = true;
+      auto first_product = [&](long long it) -> bool {
+        const int sx = (int)(it % kXStages), phx = (int)((it / kXStages) & 1), s1 = (int)(it & 1), ph1 = (int)((it >> 1) & 1);
+        if (!mbar_wait(smem_u32(&misc->full_x[sx]), phx)) { atomicCAS(status, 0u, 0x610u + sx); return false; }
+        if (!mbar_wait(smem_u32(&misc->d1_empty[s1]), ph1 ^ 1)) { atomicCAS(status, 0u, 0x620u + s1); return false; }
+        tc_fence_after();
+        const uint32_t a_base = smem_base + kOffX + sx * kStageBytes, b_base = smem_base + kOffR;
+        for (int u = 0; u < slices; ++u) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            mma_f16_ss(tmem + s1 * 128 + u * 64, umma_smem_desc_sw128(a_base + u * kAtomBytes + ks * 32, 16, 1024),
+                       umma_smem_desc_sw128(b_base + ks * 32, 16, 1024), idesc1, ks > 0);
+        }
+        mma_commit(smem_u32(&misc->empty_x[sx]));
+        mma_commit(smem_u32(&misc->d1_full[s1]));
+        return true;
+      };
+      auto second_product = [&](long long it) -> bool {
+        const int s = (int)(it & 1), ph = (int)((it >> 1) & 1);
+        if (!mbar_wait(smem_u32(&misc->y_full[s]), ph)) { atomicCAS(status, 0u, 0x630u + s); return false; }
+        if (!mbar_wait(smem_u32(&misc->d2_empty), (uint32_t)((it & 1) ^ 1))) { atomicCAS(status, 0u, 0x640u); return false; }
+        tc_fence_after();
+        const uint32_t a_base = smem_base + kOffLL, b_base = smem_base + kOffY + s * kStageBytes;
+        for (int ks = 0; ks < m / 16; ++ks)
+          mma_f16_ss(tmem + kColZ, umma_smem_desc_sw128(a_base + ks * 32, 16, 1024),
+                     umma_smem_desc_sw128(b_base + ks * 2048, (uint32_t)(m * 128), 1024), idesc2, ks > 0);
+        mma_commit(smem_u32(&misc->y_empty[s]));
+        mma_commit(smem_u32(&misc->d2_full));
+        return true;
+      };
+      if (mine > 0) ok = first_product(0);
+      for (long long it = 0; ok && it < mine; ++it) {
+        if (it + 1 < mine) ok = first_product(it + 1);
+        if (ok) ok = second_product(it);
+      }
+    }
+  } else if (warp < 6) {
+    // ---- Y pass ------------------------------------------------------------------------------------------
+    const int q = warp & 3, r = q * 32 + lane;
+    int it = 0;
+    for (long long grp = blockIdx.x; grp < ngroups; grp += gridDim.x, ++it) {
+      const int s = it & 1, ph = (it >> 1) & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&misc->d1_full[s]), ph))) { atomicCAS(status, 0u, 0x700u + s); break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&misc->y_empty[s]), ph ^ 1))) { atomicCAS(status, 0u, 0x710u + s); break; }
+      tc_fence_after();
+      for (int u = 0; u < slices; ++u) {
+        const int row = u * 128 + r;
+        uint32_t v0[32], v1[32];
+        const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + s * 128 + u * 64;
+        tmem_ld_32x32b_x32(taddr, v0);
+        tmem_ld_32x32b_x32(taddr + 32, v1);
+        tmem_ld_wait();
+        if (row < rows_group) {
+          uint8_t* yrow = smem + kOffY + s * kStageBytes + row * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t* v = j < 4 ? v0 : v1;
+            const int b = (j & 3) * 8;
+            uint4 w;
+            w.x = pack2<T>(__uint_as_float(v[b + 0]), __uint_as_float(v[b + 1]));
+            w.y = pack2<T>(__uint_as_float(v[b + 2]), __uint_as_float(v[b + 3]));
+            w.z = pack2<T>(__uint_as_float(v[b + 4]), __uint_as_float(v[b + 5]));
+            w.w = pack2<T>(__uint_as_float(v[b + 6]), __uint_as_float(v[b + 7]));
+            *reinterpret_cast<uint4*>(yrow + ((j ^ (row & 7)) << 4)) = w;
+          }
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(smem_u32(&misc->d1_empty[s]));
+      mbar_arrive(smem_u32(&misc->y_full[s]));
+    }
+  } else {
+    // ---- quantize pass -----------------------------------------------------------------------------------
+    const int e = (warp - 6) >> 2, q = warp & 3, l = q * 32 + lane;
+    const int c = l / m, mi = l - c * m;
+    const int t_local = e * copies + c;
+    const bool active = c < copies && t_local < kGroup;
+    const bool warp_uniform = (m & 31) == 0;
+    const int feat = m * 64;
+    int it = 0;
+    for (long long grp = blockIdx.x; grp < ngroups; grp += gridDim.x, ++it) {
+      const int ph = it & 1, buf = it % 3;
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&misc->d2_full), ph))) { atomicCAS(status, 0u, 0x800u + e); break; }
+      tc_fence_after();
+      const long long tok = grp * kGroup + t_local;
+      const bool valid = active && tok < tokens;
+      const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + kColZ + (active ? t_local : 0) * 64;
+      uint32_t v0[32], v1[32];
+      tmem_ld_32x32b_x32(taddr, v0);
+      tmem_ld_32x32b_x32(taddr + 32, v1);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&misc->d2_empty));  // the Z accumulators are free for the next group
+
+      float s = 1.f, inv_s = 1.f;
+      if (MODE != kTransform) {
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(v0[i])), fabsf(__uint_as_float(v1[i]))));
+        if (!valid) amax = 0.f;
+        amax = DT<T>::rnd(amax);
+        if (warp_uniform) {
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+          if (lane == 0 && active) atomicMax(&misc->absmax_bits[e][buf][c], __float_as_int(amax));
+        } else if (active) {
+          atomicMax(&misc->absmax_bits[e][buf][c], __float_as_int(amax));
+        }
+        const uint32_t gs = smem_u32(&misc->group_sync[e]);
+        mbar_arrive(gs);
+        if (!__all_sync(0xffffffffu, mbar_wait(gs, ph))) { atomicCAS(status, 0u, 0x810u + e); break; }
+        if (active) amax = __int_as_float(misc->absmax_bits[e][buf][c]);
+        if (l < 8) misc->absmax_bits[e][(it + 2) % 3][l] = 0;
+        const float top = DT<T>::rnd(amax * clip);
+        s = fmaxf(DT<T>::rnd(__fdiv_rn(top, 7.0f)), DT<T>::floor_scale());
+        inv_s = __frcp_rn(s);
+        if (valid && mi == 0) store_scale(scales, tok, s, scale_dtype);
+      }
+      const bool zero_scale = (MODE != kTransform) && (s == 0.f);
+
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t(&v)[32] = half ? v1 : v0;
+        const int c0 = half * 32;
+        if (MODE == kTransform) {
+          if (valid) {
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + tok * feat + mi * 64 + c0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              dst[j] = make_float4(DT<T>::rnd(__uint_as_float(v[4 * j])), DT<T>::rnd(__uint_as_float(v[4 * j + 1])),
+                                   DT<T>::rnd(__uint_as_float(v[4 * j + 2])), DT<T>::rnd(__uint_as_float(v[4 * j + 3])));
+          }
+        } else {
+          uint32_t pb[4], qb[4];
+          if (!zero_scale) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) nibble_bytes<T>(v, 8 * j, s, inv_s, pb[j], qb[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              pb[j] = qb[j] = 0;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float z0 = DT<T>::rnd(__uint_as_float(v[8 * j + i])), z1 = DT<T>::rnd(__uint_as_float(v[8 * j + 4 + i]));
+                pb[j] |= (uint32_t)(z0 > 0.f ? 15 : (z0 < 0.f ? 0 : 8)) << (8 * i);
+                qb[j] |= (uint32_t)(z1 > 0.f ? 15 : (z1 < 0.f ? 0 : 8)) << (8 * i);
+              }
+            }
+          }
+          if (MODE == kPacked) {
+            if (valid) {
+              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(out) + tok * (feat / 8) + (mi * 64 + c0) / 8);
+              *dst = make_uint4(pack8(pb[0], qb[0]), pack8(pb[1], qb[1]), pack8(pb[2], qb[2]), pack8(pb[3], qb[3]));
+            }
+          } else if (valid) {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<int8_t*>(out) + tok * feat + mi * 64 + c0);
+            dst[0] = make_uint4(bytes4(pb[0]), bytes4(qb[0]), bytes4(pb[1]), bytes4(qb[1]));
+            dst[1] = make_uint4(bytes4(pb[2]), bytes4(qb[2]), bytes4(pb[3]), bytes4(qb[3]));
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+template <typename T, int MODE>
+int launch_one(const CUtensorMap& map, const void* left, const void* right, void* out, void* scales, int64_t tokens, int m,
+               float clip, int scale_dtype, uint32_t* status, cudaStream_t stream) {
+  auto kern = flatquant_n64_kernel<T, MODE>;
+  int dev = 0, sms = 148;
+  QO_CUDA_TRY(cudaGetDevice(&dev));
+  static bool configured[64] = {};
+  if (!configured[dev & 63]) {
+    QO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    configured[dev & 63] = true;
+  }
+  QO_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int64_t ngroups = (tokens + kGroup - 1) / kGroup;
+  const int grid = (int)(ngroups < sms ? ngroups : sms);
+  kern<<<grid, kThreads, kSmemBytes, stream>>>(map, reinterpret_cast<const T*>(left), reinterpret_cast<const T*>(right), out,
+                                               scales, (long long)tokens, m, clip, scale_dtype, status);
+  return check_launch("flatquant_n64_kernel");
+}
+
+template <typename T>
+int launch_mode(int mode, const CUtensorMap& map, const void* left, const void* right, void* out, void* scales,
+                int64_t tokens, int m, float clip, int scale_dtype, uint32_t* status, cudaStream_t stream) {
+  switch (mode) {
+    case kInt8: return launch_one<T, kInt8>(map, left, right, out, scales, tokens, m, clip, scale_dtype, status, stream);
+    case kPacked: return launch_one<T, kPacked>(map, left, right, out, scales, tokens, m, clip, scale_dtype, status, stream);
+    default: return launch_one<T, kTransform>(map, left, right, out, scales, tokens, m, clip, scale_dtype, status, stream);
+  }
+}
+
+}  // namespace
+
+bool flatquant_sm100_n64_supported(int m, int n) { return n == 64 && m >= 16 && m <= 64 && (m % 16) == 0; }
+
+int launch_flatquant_sm100_n64(int mode, const void* x_map, const void* left, const void* right, void* out, void* scales,
+                               int64_t tokens, int m, float clip, int in_dtype, int scale_dtype, uint32_t* status,
+                               cudaStream_t stream) {
+  const CUtensorMap& map = *reinterpret_cast<const CUtensorMap*>(x_map);
+  if (in_dtype == QO_BF16)
+    return launch_mode<__nv_bfloat16>(mode, map, left, right, out, scales, tokens, m, clip, scale_dtype, status, stream);
+  return launch_mode<__half>(mode, map, left, right, out, scales, tokens, m, clip, scale_dtype, status, stream);
+}
+
+}  // namespace qo

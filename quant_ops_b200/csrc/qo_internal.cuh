@@ -122,7 +122,8 @@ int launch_flatquant_generic(const void* x, int64_t ldx, const void* left, const
 int launch_flatquant_sm100(const void* x, int64_t ldx, const void* left, const void* right, void* codes,
                            void* scales, int64_t tokens, int m, int n, float clip, int in_dtype, int pack,
                            int scale_dtype, cudaStream_t stream);
-bool flatquant_sm100_supported(int64_t ldx, int m, int n, int in_dtype, const void* x, float clip);
+bool flatquant_sm100_supported(int64_t ldx, int m, int n, int in_dtype, const void* x, const void* left, const void* right,
+                               float clip);
 // mode: 0 int8 codes, 1 packed codes, 2 transform only (float32 Z written to `codes`)
 int launch_flatquant_sm100_mode(int mode, const void* x, int64_t ldx, const void* left, const void* right, void* codes,
                                 void* scales, int64_t tokens, int m, int n, float clip, int in_dtype, int scale_dtype,
