@@ -18,6 +18,7 @@
 //
 // Rounding points and the exactness arguments are those of flatquant_sm100.cu (reference:
 // src/quant_ops/ops/quantization/flatquant/ops.py:99-117).  Every mbarrier wait is bounded.
+#include <cstdlib>
 #include "flatquant_sm100_common.cuh"
 
 namespace qo {
@@ -50,7 +51,7 @@ template <typename T, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restrict__ left, const T* __restrict__ right,
                      void* __restrict__ out, void* __restrict__ scales, long long tokens, int m, float clip,
-                     int scale_dtype, uint32_t* __restrict__ status) {
+                     int scale_dtype, uint32_t* __restrict__ status, uint32_t flags) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Misc* misc = reinterpret_cast<Misc*>(smem + kOffMisc);
@@ -107,29 +108,33 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
         if (c < l_chunks) reinterpret_cast<uint4*>(raw_l)[c] = tmp[i];
         else if (c - l_chunks < r_chunks) reinterpret_cast<uint4*>(raw_r)[c - l_chunks] = tmp[i];
       }
-      for (int idx = t13; idx < kAtomBytes / 16; idx += kStagers) reinterpret_cast<uint4*>(smem + kOffLL)[idx] = make_uint4(0, 0, 0, 0);
     }
     asm volatile("bar.sync 1, %0;" ::"n"(kStagers) : "memory");
-    // R^T, K-major: row = output column n, k = j along the row
-    for (int c = t13; c < 64 * 64 / 8; c += kStagers) {
-      const int j = c >> 3, n0 = (c & 7) * 8;
-      const uint4 v = reinterpret_cast<const uint4*>(raw_r)[c];
-      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    // R^T, K-major: row = output column n; its 16-byte chunk jc holds R[8jc .. 8jc+7][n].  Lanes walk n, so the
+    // 2-byte reads of a warp are contiguous and each thread makes one 16-byte swizzled store.
+    for (int idx = t13; idx < 64 * 8; idx += kStagers) {
+      const int n = idx & 63, jc = idx >> 6;
+      uint32_t w[4];
 #pragma unroll
-      for (int e8 = 0; e8 < 8; ++e8) {
-        const int n = n0 + e8;
-        const uint32_t off = (n >> 3) * 1024 + (n & 7) * 128 + (((j >> 3) ^ (n & 7)) << 4) + (j & 7) * 2;
-        *reinterpret_cast<uint16_t*>(smem + kOffR + off) = (uint16_t)(w[e8 >> 1] >> (16 * (e8 & 1)));
-      }
+      for (int e2 = 0; e2 < 4; ++e2)
+        w[e2] = (uint32_t)raw_r[(8 * jc + 2 * e2) * 64 + n] | ((uint32_t)raw_r[(8 * jc + 2 * e2 + 1) * 64 + n] << 16);
+      *reinterpret_cast<uint4*>(smem + kOffR + (n >> 3) * 1024 + (n & 7) * 128 + ((jc ^ (n & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
     }
-    // LL, K-major: row (copy, i), column k holds L[k][i]
+    // LL, K-major: row (copy, i), column k holds L[k][i]; rows past the last copy and columns past m are zero
     const int ll_rows = copies * m;
-    for (int idx = t13; idx < ll_rows * m; idx += kStagers) {
-      const int k = idx / ll_rows, r = idx - k * ll_rows;
+    for (int idx = t13; idx < 128 * 8; idx += kStagers) {
+      const int r = idx & 127, kc = idx >> 7;
       int i = r;
       while (i >= m) i -= m;
-      const uint32_t off = (r >> 3) * 1024 + (r & 7) * 128 + (((k >> 3) ^ (r & 7)) << 4) + (k & 7) * 2;
-      *reinterpret_cast<uint16_t*>(smem + kOffLL + off) = raw_l[k * m + i];
+      uint32_t w[4];
+#pragma unroll
+      for (int e2 = 0; e2 < 4; ++e2) {
+        const int k0 = 8 * kc + 2 * e2;
+        const uint32_t lo = (r < ll_rows && k0 < m) ? raw_l[k0 * m + i] : 0u;
+        const uint32_t hi = (r < ll_rows && k0 + 1 < m) ? raw_l[(k0 + 1) * m + i] : 0u;
+        w[e2] = lo | (hi << 16);
+      }
+      *reinterpret_cast<uint4*>(smem + kOffLL + (r >> 3) * 1024 + (r & 7) * 128 + ((kc ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
     }
     fence_proxy_async_smem();
     asm volatile("bar.sync 1, %0;" ::"n"(kStagers) : "memory");
@@ -341,7 +346,7 @@ int launch_one(const CUtensorMap& map, const void* left, const void* right, void
   const int64_t ngroups = (tokens + kGroup - 1) / kGroup;
   const int grid = (int)(ngroups < sms ? ngroups : sms);
   kern<<<grid, kThreads, kSmemBytes, stream>>>(map, reinterpret_cast<const T*>(left), reinterpret_cast<const T*>(right), out,
-                                               scales, (long long)tokens, m, clip, scale_dtype, status);
+                                               scales, (long long)tokens, m, clip, scale_dtype, status, getenv("QO_DEBUG_FLAGS") ? (uint32_t)strtoul(getenv("QO_DEBUG_FLAGS"), nullptr, 0) : 0u);
   return check_launch("flatquant_n64_kernel");
 }
 
