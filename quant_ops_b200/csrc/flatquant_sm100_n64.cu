@@ -27,7 +27,7 @@ namespace {
 using namespace ptx;
 using namespace fq;
 
-constexpr int kThreads = 448;
+constexpr int kThreads = 480;                  // 15 warps: TMA, first-product issuer, 4 + 8 epilogue, second-product issuer
 constexpr int kGroup = 4;                      // tokens per group
 constexpr int kXStages = 3;
 constexpr int kStageBytes = 256 * 128;         // up to 4 x 64 rows of 128 bytes
@@ -86,8 +86,8 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
   tc_fence_after();
   const uint32_t tmem = misc->tmem_base;
 
-  if (warp != 0) {
-    constexpr int kStagers = kThreads - 32;
+  if (warp != 0 && warp != 14) {
+    constexpr int kStagers = 13 * 32;
     const int t13 = tid - 32;
     // raw copies of L and R into the (still unused) Y stages, all 16-byte loads in flight at once
     uint16_t* raw_l = reinterpret_cast<uint16_t*>(smem + kOffY);
@@ -154,44 +154,51 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
     }
   } else if (warp == 1) {
     if (lane == 0) {
+      // One thread feeds the tensor core, so its instruction count per MMA is on the critical path: descriptors are
+      // built once and advanced with a single add on the address field (units of 16 bytes), loops are unrolled.
       const uint32_t idesc1 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 0, 0, 128, 64);
-      const uint32_t idesc2 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 0, 1, 128, 256);
-      long long mine = 0;
-      if ((long long)blockIdx.x < ngroups) mine = (ngroups - blockIdx.x + gridDim.x - 1) / gridDim.x;
-      bool ok = true;
-      auto first_product = [&](long long it) -> bool {
-        const int sx = (int)(it % kXStages), phx = (int)((it / kXStages) & 1), s1 = (int)(it & 1), ph1 = (int)((it >> 1) & 1);
-        if (!mbar_wait(smem_u32(&misc->full_x[sx]), phx)) { atomicCAS(status, 0u, 0x610u + sx); return false; }
-        if (!mbar_wait(smem_u32(&misc->d1_empty[s1]), ph1 ^ 1)) { atomicCAS(status, 0u, 0x620u + s1); return false; }
+      const uint64_t desc_x0 = umma_smem_desc_sw128(smem_base + kOffX, 16, 1024);
+      const uint64_t desc_r = umma_smem_desc_sw128(smem_base + kOffR, 16, 1024);
+      int mine = 0;
+      if ((long long)blockIdx.x < ngroups) mine = (int)((ngroups - blockIdx.x + gridDim.x - 1) / gridDim.x);
+      int sx = 0, phx = 0;  // X stage and its phase
+      for (int it = 0; it < mine; ++it) {
+        const int s1 = it & 1, ph1 = (it >> 1) & 1;
+        if (!mbar_wait(smem_u32(&misc->full_x[sx]), phx)) { atomicCAS(status, 0u, 0x610u + sx); break; }
+        if (!mbar_wait(smem_u32(&misc->d1_empty[s1]), ph1 ^ 1)) { atomicCAS(status, 0u, 0x620u + s1); break; }
         tc_fence_after();
-        const uint32_t a_base = smem_base + kOffX + sx * kStageBytes, b_base = smem_base + kOffR;
-        for (int u = 0; u < slices; ++u) {
+        const uint64_t da = desc_x0 + (uint64_t)(sx * (kStageBytes >> 4));
+        const uint32_t d = tmem + s1 * 128;
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            mma_f16_ss(tmem + s1 * 128 + u * 64, umma_smem_desc_sw128(a_base + u * kAtomBytes + ks * 32, 16, 1024),
-                       umma_smem_desc_sw128(b_base + ks * 32, 16, 1024), idesc1, ks > 0);
+        for (int ks = 0; ks < 4; ++ks) mma_f16_ss(d, da + ks * 2, desc_r + ks * 2, idesc1, ks);
+        if (slices > 1) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) mma_f16_ss(d + 64, da + (kAtomBytes >> 4) + ks * 2, desc_r + ks * 2, idesc1, ks);
         }
         mma_commit(smem_u32(&misc->empty_x[sx]));
         mma_commit(smem_u32(&misc->d1_full[s1]));
-        return true;
-      };
-      auto second_product = [&](long long it) -> bool {
-        const int s = (int)(it & 1), ph = (int)((it >> 1) & 1);
-        if (!mbar_wait(smem_u32(&misc->y_full[s]), ph)) { atomicCAS(status, 0u, 0x630u + s); return false; }
-        if (!mbar_wait(smem_u32(&misc->d2_empty), (uint32_t)((it & 1) ^ 1))) { atomicCAS(status, 0u, 0x640u); return false; }
+        if (++sx == kXStages) { sx = 0; phx ^= 1; }
+      }
+    }
+  } else if (warp == 14) {
+    // second-product issuer: its waits and commits overlap with the first-product MMAs of later groups
+    if (lane == 0) {
+      const uint32_t idesc2 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 0, 1, 128, 256);
+      const uint64_t desc_ll = umma_smem_desc_sw128(smem_base + kOffLL, 16, 1024);
+      const uint64_t desc_y0 = umma_smem_desc_sw128(smem_base + kOffY, (uint32_t)(m * 128), 1024);
+      const int ksteps2 = m >> 4;
+      int mine = 0;
+      if ((long long)blockIdx.x < ngroups) mine = (int)((ngroups - blockIdx.x + gridDim.x - 1) / gridDim.x);
+      for (int it = 0; it < mine; ++it) {
+        const int s = it & 1, ph = (it >> 1) & 1;
+        if (!mbar_wait(smem_u32(&misc->y_full[s]), ph)) { atomicCAS(status, 0u, 0x630u + s); break; }
+        if (!mbar_wait(smem_u32(&misc->d2_empty), (uint32_t)((it & 1) ^ 1))) { atomicCAS(status, 0u, 0x640u); break; }
         tc_fence_after();
-        const uint32_t a_base = smem_base + kOffLL, b_base = smem_base + kOffY + s * kStageBytes;
-        for (int ks = 0; ks < m / 16; ++ks)
-          mma_f16_ss(tmem + kColZ, umma_smem_desc_sw128(a_base + ks * 32, 16, 1024),
-                     umma_smem_desc_sw128(b_base + ks * 2048, (uint32_t)(m * 128), 1024), idesc2, ks > 0);
+        uint64_t da2 = desc_ll, db2 = desc_y0 + (uint64_t)(s * (kStageBytes >> 4));
+#pragma unroll 1
+        for (int ks = 0; ks < ksteps2; ++ks, da2 += 2, db2 += 128) mma_f16_ss(tmem + kColZ, da2, db2, idesc2, ks);
         mma_commit(smem_u32(&misc->y_empty[s]));
         mma_commit(smem_u32(&misc->d2_full));
-        return true;
-      };
-      if (mine > 0) ok = first_product(0);
-      for (long long it = 0; ok && it < mine; ++it) {
-        if (it + 1 < mine) ok = first_product(it + 1);
-        if (ok) ok = second_product(it);
       }
     }
   } else if (warp < 6) {
@@ -203,7 +210,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&misc->d1_full[s]), ph))) { atomicCAS(status, 0u, 0x700u + s); break; }
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&misc->y_empty[s]), ph ^ 1))) { atomicCAS(status, 0u, 0x710u + s); break; }
       tc_fence_after();
-      for (int u = 0; u < slices; ++u) {
+      for (int u = 0; u < ((flags & 256u) ? 0 : slices); ++u) {
         const int row = u * 128 + r;
         uint32_t v0[32], v1[32];
         const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + s * 128 + u * 64;
@@ -252,6 +259,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(smem_u32(&misc->d2_empty));  // the Z accumulators are free for the next group
+      if (flags & 128u) continue;  // EXPERIMENT
 
       float s = 1.f, inv_s = 1.f;
       if (MODE != kTransform) {
@@ -278,6 +286,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
         if (valid && mi == 0) store_scale(scales, tok, s, scale_dtype);
       }
       const bool zero_scale = (MODE != kTransform) && (s == 0.f);
+      if (flags & 512u) continue;  // EXPERIMENT
 
 #pragma unroll
       for (int half = 0; half < 2; ++half) {

@@ -33,7 +33,9 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 // Bounded wait: gives up after `limit_cycles` SM clocks and returns false (the caller records the failure and
-// leaves); a healthy pipeline never gets near the limit.
+// leaves); a healthy pipeline never gets near the limit.  The retries pass a suspend-time hint, so a waiting thread
+// is parked by the hardware until the phase completes instead of competing for issue slots with the warp that
+// feeds the tensor core.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, long long limit_cycles = 4000000000LL) {
   uint32_t ok = 0;
   asm volatile(
@@ -46,9 +48,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, long lo
   while (true) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}\n"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(200000u) : "memory");
     if (ok) return true;
     if (clock64() - t0 > limit_cycles) return false;
   }
