@@ -521,8 +521,8 @@ int launch_flatquant_sm100_mode(int mode, const void* x, int64_t ldx, const void
   CUtensorMap map;
   const cuuint64_t dims[3] = {(cuuint64_t)n, (cuuint64_t)m, (cuuint64_t)tokens};
   const cuuint64_t strides[2] = {(cuuint64_t)n * 2, (cuuint64_t)ldx * 2};
-  const bool batched = flatquant_sm100_n64_supported(m, n);  // groups of 4 tokens, wide second product
-  const cuuint32_t box[3] = {64, (cuuint32_t)m, (cuuint32_t)(batched ? 4 : 128 / m)};
+  const bool batched = flatquant_sm100_n64_supported(m, n);  // groups of 2 tokens, stacked-L^T second product
+  const cuuint32_t box[3] = {64, (cuuint32_t)m, (cuuint32_t)(batched ? 2 : 128 / m)};
   const cuuint32_t estr[3] = {1, 1, 1};
   const CUresult r = encode_fn()(&map, in_dtype == QO_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
                                  3, const_cast<void*>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,

@@ -18,7 +18,6 @@
 //
 // Rounding points and the exactness arguments are those of flatquant_sm100.cu (reference:
 // src/quant_ops/ops/quantization/flatquant/ops.py:99-117).  Every mbarrier wait is bounded.
-#include <cstdlib>
 #include "flatquant_sm100_common.cuh"
 
 namespace qo {
@@ -27,22 +26,24 @@ namespace {
 using namespace ptx;
 using namespace fq;
 
-constexpr int kThreads = 480;                  // 15 warps: TMA, first-product issuer, 4 + 8 epilogue, second-product issuer
-constexpr int kGroup = 4;                      // tokens per group
-constexpr int kXStages = 3;
-constexpr int kStageBytes = 256 * 128;         // up to 4 x 64 rows of 128 bytes
+constexpr int kThreads = 480;                  // 15 warps: TMA, first-product issuer, 4 + 4 + 4 epilogue, second-product issuer
+constexpr int kGroup = 2;                      // tokens per group
+constexpr int kXStages = 6;
+constexpr int kYStages = 3;                    // also the number of Y accumulator stages
+constexpr int kStageBytes = 128 * 128;         // up to 2 x 64 rows of 128 bytes
 constexpr int kOffX = 0;
 constexpr int kOffY = kOffX + kXStages * kStageBytes;
-constexpr int kOffR = kOffY + 2 * kStageBytes;
+constexpr int kOffR = kOffY + kYStages * kStageBytes;
 constexpr int kOffLL = kOffR + 64 * 128;
 constexpr int kOffMisc = kOffLL + kAtomBytes;
 constexpr int kSmemBytes = kOffMisc + 1024 + 1024;
-constexpr int kTmemCols = 512;                 // Y accumulators: 2 stages x 128 columns; Z accumulators: 256 columns
+constexpr int kTmemCols = 512;                 // Y accumulators: 3 stages x 64 columns; Z accumulators: 2 stages x 128
 constexpr int kColZ = 256;
 
 struct Misc {
   uint64_t full_x[kXStages], empty_x[kXStages];
-  uint64_t d1_full[2], d1_empty[2], y_full[2], y_empty[2], d2_full, d2_empty, group_sync[2];
+  uint64_t d1_full[kYStages], d1_empty[kYStages], y_full[kYStages], y_empty[kYStages];
+  uint64_t d2_full[2], d2_empty[2], set_sync[2];
   uint32_t tmem_base;
   int absmax_bits[2][3][8];
 };
@@ -51,28 +52,31 @@ template <typename T, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restrict__ left, const T* __restrict__ right,
                      void* __restrict__ out, void* __restrict__ scales, long long tokens, int m, float clip,
-                     int scale_dtype, uint32_t* __restrict__ status, uint32_t flags) {
+                     int scale_dtype, uint32_t* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Misc* misc = reinterpret_cast<Misc*>(smem + kOffMisc);
   const uint32_t smem_base = smem_u32(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int copies = 128 / m;                 // copies of L^T stacked in the A operand of the second product
-  const int rows_group = kGroup * m;          // X / Y rows per group
-  const int slices = (rows_group + 127) >> 7; // 128-row slices of the first product
+  const int copies = 128 / m;                 // copies of L^T stacked in the A operand of the second product (>= 2)
+  const int rows_group = kGroup * m;          // X / Y rows per group (<= 128)
   const long long ngroups = (tokens + kGroup - 1) / kGroup;
+  int mine = 0;                               // groups this CTA works on
+  if ((long long)blockIdx.x < ngroups) mine = (int)((ngroups - blockIdx.x + gridDim.x - 1) / gridDim.x);
 
   if (tid == 0) {
     for (int i = 0; i < kXStages; ++i) { mbar_init(smem_u32(&misc->full_x[i]), 1); mbar_init(smem_u32(&misc->empty_x[i]), 1); }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kYStages; ++i) {
       mbar_init(smem_u32(&misc->d1_full[i]), 1);
       mbar_init(smem_u32(&misc->d1_empty[i]), 128);
       mbar_init(smem_u32(&misc->y_full[i]), 128);
       mbar_init(smem_u32(&misc->y_empty[i]), 1);
-      mbar_init(smem_u32(&misc->group_sync[i]), 128);
     }
-    mbar_init(smem_u32(&misc->d2_full), 1);
-    mbar_init(smem_u32(&misc->d2_empty), 256);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&misc->d2_full[i]), 1);
+      mbar_init(smem_u32(&misc->d2_empty[i]), 128);
+      mbar_init(smem_u32(&misc->set_sync[i]), 128);
+    }
     for (int i = 0; i < 2 * 3 * 8; ++i) (&misc->absmax_bits[0][0][0])[i] = 0;
     fence_barrier_init();
     prefetch_tensormap(&x_map);
@@ -143,131 +147,124 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
   if (warp == 0) {
     if (lane == 0) {
       const uint32_t bytes = (uint32_t)(rows_group * 128);
-      int it = 0;
-      for (long long grp = blockIdx.x; grp < ngroups; grp += gridDim.x, ++it) {
-        const int s = it % kXStages, ph = (it / kXStages) & 1;
+      int s = 0, ph = 0;
+      long long grp = blockIdx.x;
+      for (int it = 0; it < mine; ++it, grp += gridDim.x) {
         if (!mbar_wait(smem_u32(&misc->empty_x[s]), ph ^ 1)) { atomicCAS(status, 0u, 0x600u + s); break; }
         const uint32_t bar = smem_u32(&misc->full_x[s]);
         mbar_arrive_expect_tx(bar, bytes);
         tma_load_3d(smem_base + kOffX + s * kStageBytes, &x_map, bar, 0, 0, (int)(grp * kGroup));
+        if (++s == kXStages) { s = 0; ph ^= 1; }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      // One thread feeds the tensor core, so its instruction count per MMA is on the critical path: descriptors are
-      // built once and advanced with a single add on the address field (units of 16 bytes), loops are unrolled.
+      // One thread feeds the tensor core, so its instruction count per MMA matters: descriptors are built once and
+      // advanced with a single add on the address field (units of 16 bytes).
       const uint32_t idesc1 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 0, 0, 128, 64);
       const uint64_t desc_x0 = umma_smem_desc_sw128(smem_base + kOffX, 16, 1024);
       const uint64_t desc_r = umma_smem_desc_sw128(smem_base + kOffR, 16, 1024);
-      int mine = 0;
-      if ((long long)blockIdx.x < ngroups) mine = (int)((ngroups - blockIdx.x + gridDim.x - 1) / gridDim.x);
-      int sx = 0, phx = 0;  // X stage and its phase
+      int sx = 0, phx = 0, s1 = 0, ph1 = 0;
       for (int it = 0; it < mine; ++it) {
-        const int s1 = it & 1, ph1 = (it >> 1) & 1;
         if (!mbar_wait(smem_u32(&misc->full_x[sx]), phx)) { atomicCAS(status, 0u, 0x610u + sx); break; }
         if (!mbar_wait(smem_u32(&misc->d1_empty[s1]), ph1 ^ 1)) { atomicCAS(status, 0u, 0x620u + s1); break; }
         tc_fence_after();
         const uint64_t da = desc_x0 + (uint64_t)(sx * (kStageBytes >> 4));
-        const uint32_t d = tmem + s1 * 128;
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) mma_f16_ss(d, da + ks * 2, desc_r + ks * 2, idesc1, ks);
-        if (slices > 1) {
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks) mma_f16_ss(d + 64, da + (kAtomBytes >> 4) + ks * 2, desc_r + ks * 2, idesc1, ks);
-        }
+        for (int ks = 0; ks < 4; ++ks) mma_f16_ss(tmem + s1 * 64, da + ks * 2, desc_r + ks * 2, idesc1, ks);
         mma_commit(smem_u32(&misc->empty_x[sx]));
         mma_commit(smem_u32(&misc->d1_full[s1]));
         if (++sx == kXStages) { sx = 0; phx ^= 1; }
+        if (++s1 == kYStages) { s1 = 0; ph1 ^= 1; }
       }
     }
   } else if (warp == 14) {
     // second-product issuer: its waits and commits overlap with the first-product MMAs of later groups
     if (lane == 0) {
-      const uint32_t idesc2 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 0, 1, 128, 256);
+      const uint32_t idesc2 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 0, 1, 128, 128);
       const uint64_t desc_ll = umma_smem_desc_sw128(smem_base + kOffLL, 16, 1024);
       const uint64_t desc_y0 = umma_smem_desc_sw128(smem_base + kOffY, (uint32_t)(m * 128), 1024);
       const int ksteps2 = m >> 4;
-      int mine = 0;
-      if ((long long)blockIdx.x < ngroups) mine = (int)((ngroups - blockIdx.x + gridDim.x - 1) / gridDim.x);
+      int sy = 0, phy = 0;
       for (int it = 0; it < mine; ++it) {
-        const int s = it & 1, ph = (it >> 1) & 1;
-        if (!mbar_wait(smem_u32(&misc->y_full[s]), ph)) { atomicCAS(status, 0u, 0x630u + s); break; }
-        if (!mbar_wait(smem_u32(&misc->d2_empty), (uint32_t)((it & 1) ^ 1))) { atomicCAS(status, 0u, 0x640u); break; }
+        const int e = it & 1, ph = (it >> 1) & 1;
+        if (!mbar_wait(smem_u32(&misc->y_full[sy]), phy)) { atomicCAS(status, 0u, 0x630u + sy); break; }
+        if (!mbar_wait(smem_u32(&misc->d2_empty[e]), ph ^ 1)) { atomicCAS(status, 0u, 0x640u + e); break; }
         tc_fence_after();
-        uint64_t da2 = desc_ll, db2 = desc_y0 + (uint64_t)(s * (kStageBytes >> 4));
+        uint64_t da2 = desc_ll, db2 = desc_y0 + (uint64_t)(sy * (kStageBytes >> 4));
 #pragma unroll 1
-        for (int ks = 0; ks < ksteps2; ++ks, da2 += 2, db2 += 128) mma_f16_ss(tmem + kColZ, da2, db2, idesc2, ks);
-        mma_commit(smem_u32(&misc->y_empty[s]));
-        mma_commit(smem_u32(&misc->d2_full));
+        for (int ks = 0; ks < ksteps2; ++ks, da2 += 2, db2 += 128) mma_f16_ss(tmem + kColZ + e * 128, da2, db2, idesc2, ks);
+        mma_commit(smem_u32(&misc->y_empty[sy]));
+        mma_commit(smem_u32(&misc->d2_full[e]));
+        if (++sy == kYStages) { sy = 0; phy ^= 1; }
       }
     }
   } else if (warp < 6) {
-    // ---- Y pass ------------------------------------------------------------------------------------------
+    // ---- Y pass: row r of the group = tensor-memory lane r -------------------------------------------------
     const int q = warp & 3, r = q * 32 + lane;
-    int it = 0;
-    for (long long grp = blockIdx.x; grp < ngroups; grp += gridDim.x, ++it) {
-      const int s = it & 1, ph = (it >> 1) & 1;
+    int s = 0, ph = 0;
+    for (int it = 0; it < mine; ++it) {
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&misc->d1_full[s]), ph))) { atomicCAS(status, 0u, 0x700u + s); break; }
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&misc->y_empty[s]), ph ^ 1))) { atomicCAS(status, 0u, 0x710u + s); break; }
       tc_fence_after();
-      for (int u = 0; u < ((flags & 256u) ? 0 : slices); ++u) {
-        const int row = u * 128 + r;
-        uint32_t v0[32], v1[32];
-        const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + s * 128 + u * 64;
-        tmem_ld_32x32b_x32(taddr, v0);
-        tmem_ld_32x32b_x32(taddr + 32, v1);
-        tmem_ld_wait();
-        if (row < rows_group) {
-          uint8_t* yrow = smem + kOffY + s * kStageBytes + row * 128;
+      uint32_t v0[32], v1[32];
+      const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + s * 64;
+      tmem_ld_32x32b_x32(taddr, v0);
+      tmem_ld_32x32b_x32(taddr + 32, v1);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&misc->d1_empty[s]));  // accumulators are in registers: the stage can be overwritten
+      if (r < rows_group) {
+        uint8_t* yrow = smem + kOffY + s * kStageBytes + r * 128;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint32_t* v = j < 4 ? v0 : v1;
-            const int b = (j & 3) * 8;
-            uint4 w;
-            w.x = pack2<T>(__uint_as_float(v[b + 0]), __uint_as_float(v[b + 1]));
-            w.y = pack2<T>(__uint_as_float(v[b + 2]), __uint_as_float(v[b + 3]));
-            w.z = pack2<T>(__uint_as_float(v[b + 4]), __uint_as_float(v[b + 5]));
-            w.w = pack2<T>(__uint_as_float(v[b + 6]), __uint_as_float(v[b + 7]));
-            *reinterpret_cast<uint4*>(yrow + ((j ^ (row & 7)) << 4)) = w;
-          }
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t* v = j < 4 ? v0 : v1;
+          const int b = (j & 3) * 8;
+          uint4 w;
+          w.x = pack2<T>(__uint_as_float(v[b + 0]), __uint_as_float(v[b + 1]));
+          w.y = pack2<T>(__uint_as_float(v[b + 2]), __uint_as_float(v[b + 3]));
+          w.z = pack2<T>(__uint_as_float(v[b + 4]), __uint_as_float(v[b + 5]));
+          w.w = pack2<T>(__uint_as_float(v[b + 6]), __uint_as_float(v[b + 7]));
+          *reinterpret_cast<uint4*>(yrow + ((j ^ (r & 7)) << 4)) = w;
         }
       }
-      tc_fence_before();
       fence_proxy_async_smem();
-      mbar_arrive(smem_u32(&misc->d1_empty[s]));
       mbar_arrive(smem_u32(&misc->y_full[s]));
+      if (++s == kYStages) { s = 0; ph ^= 1; }
     }
   } else {
-    // ---- quantize pass -----------------------------------------------------------------------------------
+    // ---- quantize pass: set e (4 warps) takes the groups with (it & 1) == e ----------------------------------
     const int e = (warp - 6) >> 2, q = warp & 3, l = q * 32 + lane;
-    const int c = l / m, mi = l - c * m;
-    const int t_local = e * copies + c;
-    const bool active = c < copies && t_local < kGroup;
+    const int c = l / m, mi = l - c * m;            // lane block c holds a copy of the Z rows: it serves token c
+    const bool active = c < kGroup;
     const bool warp_uniform = (m & 31) == 0;
     const int feat = m * 64;
-    int it = 0;
-    for (long long grp = blockIdx.x; grp < ngroups; grp += gridDim.x, ++it) {
-      const int ph = it & 1, buf = it % 3;
-      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&misc->d2_full), ph))) { atomicCAS(status, 0u, 0x800u + e); break; }
+    long long grp = (long long)blockIdx.x + (long long)e * gridDim.x;
+    for (int use = 0, it = e; it < mine; it += 2, ++use, grp += 2LL * gridDim.x) {
+      const int ph = use & 1, buf = use % 3;
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&misc->d2_full[e]), ph))) { atomicCAS(status, 0u, 0x800u + e); break; }
       tc_fence_after();
-      const long long tok = grp * kGroup + t_local;
+      const long long tok = grp * kGroup + c;
       const bool valid = active && tok < tokens;
-      const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + kColZ + (active ? t_local : 0) * 64;
+      const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + kColZ + e * 128 + (active ? c : 0) * 64;
       uint32_t v0[32], v1[32];
       tmem_ld_32x32b_x32(taddr, v0);
       tmem_ld_32x32b_x32(taddr + 32, v1);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(smem_u32(&misc->d2_empty));  // the Z accumulators are free for the next group
-      if (flags & 128u) continue;  // EXPERIMENT
+      mbar_arrive(smem_u32(&misc->d2_empty[e]));  // the Z accumulators of this stage are free again
 
       float s = 1.f, inv_s = 1.f;
       if (MODE != kTransform) {
-        float amax = 0.f;
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;  // four chains keep the dependent-latency short
 #pragma unroll
-        for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(v0[i])), fabsf(__uint_as_float(v1[i]))));
-        if (!valid) amax = 0.f;
-        amax = DT<T>::rnd(amax);
+        for (int i = 0; i < 32; i += 2) {
+          a0 = fmaxf(a0, fabsf(__uint_as_float(v0[i])));
+          a1 = fmaxf(a1, fabsf(__uint_as_float(v0[i + 1])));
+          a2 = fmaxf(a2, fabsf(__uint_as_float(v1[i])));
+          a3 = fmaxf(a3, fabsf(__uint_as_float(v1[i + 1])));
+        }
+        float amax = valid ? fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) : 0.f;
         if (warp_uniform) {
 #pragma unroll
           for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -275,18 +272,21 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
         } else if (active) {
           atomicMax(&misc->absmax_bits[e][buf][c], __float_as_int(amax));
         }
-        const uint32_t gs = smem_u32(&misc->group_sync[e]);
+        // the 128 threads of the set meet here (bounded); afterwards the slot holds the token's absmax
+        const uint32_t gs = smem_u32(&misc->set_sync[e]);
         mbar_arrive(gs);
         if (!__all_sync(0xffffffffu, mbar_wait(gs, ph))) { atomicCAS(status, 0u, 0x810u + e); break; }
         if (active) amax = __int_as_float(misc->absmax_bits[e][buf][c]);
-        if (l < 8) misc->absmax_bits[e][(it + 2) % 3][l] = 0;
-        const float top = DT<T>::rnd(amax * clip);
-        s = fmaxf(DT<T>::rnd(__fdiv_rn(top, 7.0f)), DT<T>::floor_scale());
+        if (l < 8) misc->absmax_bits[e][(use + 2) % 3][l] = 0;
+        // max of the rounded values = rounded max; clip * absmax and the division by 7 are rounded like the reference.
+        // top / 7 can neither hit nor come within 2^-13 (relative) of a midpoint of the 16-bit format, so the
+        // float32 product with 1/7 rounds to the same 16-bit value as the exact quotient.
+        const float top = DT<T>::rnd(DT<T>::rnd(amax) * clip);
+        s = fmaxf(DT<T>::rnd(top * 0.142857149f), DT<T>::floor_scale());
         inv_s = __frcp_rn(s);
         if (valid && mi == 0) store_scale(scales, tok, s, scale_dtype);
       }
       const bool zero_scale = (MODE != kTransform) && (s == 0.f);
-      if (flags & 512u) continue;  // EXPERIMENT
 
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
@@ -306,6 +306,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
 #pragma unroll
             for (int j = 0; j < 4; ++j) nibble_bytes<T>(v, 8 * j, s, inv_s, pb[j], qb[j]);
           } else {
+            // the reference divides by zero here: +-inf clamps to 7 / -8, 0/0 counts as 0
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               pb[j] = qb[j] = 0;
@@ -355,7 +356,7 @@ int launch_one(const CUtensorMap& map, const void* left, const void* right, void
   const int64_t ngroups = (tokens + kGroup - 1) / kGroup;
   const int grid = (int)(ngroups < sms ? ngroups : sms);
   kern<<<grid, kThreads, kSmemBytes, stream>>>(map, reinterpret_cast<const T*>(left), reinterpret_cast<const T*>(right), out,
-                                               scales, (long long)tokens, m, clip, scale_dtype, status, getenv("QO_DEBUG_FLAGS") ? (uint32_t)strtoul(getenv("QO_DEBUG_FLAGS"), nullptr, 0) : 0u);
+                                               scales, (long long)tokens, m, clip, scale_dtype, status);
   return check_launch("flatquant_n64_kernel");
 }
 
