@@ -38,6 +38,12 @@ __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
 //                    product with two FMAs, which gives the correctly rounded quotient (Markstein)
 template <typename T> struct P2;
 template <> struct P2<__nv_bfloat16> {
+  // |result| = max(|a|, |b|) per half (the sign is the xor of the signs and is ignored by the caller)
+  static __device__ __forceinline__ uint32_t absmax(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+  }
   static constexpr uint32_t kByteMask = 0x0F0F0F0Fu;  // the nibble's byte also carries exponent bits
   static __device__ __forceinline__ uint32_t cvt(float lo, float hi) {
     uint32_t d;
@@ -58,6 +64,11 @@ template <> struct P2<__nv_bfloat16> {
   static __device__ __forceinline__ uint32_t quot(float z0, float z1, float, float inv_s) { return cvt(z0 * inv_s, z1 * inv_s); }
 };
 template <> struct P2<__half> {
+  static __device__ __forceinline__ uint32_t absmax(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("max.xorsign.abs.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+  }
   static constexpr uint32_t kByteMask = 0xFFFFFFFFu;
   static __device__ __forceinline__ uint32_t cvt(float lo, float hi) {
     uint32_t d;
@@ -95,6 +106,15 @@ __device__ __forceinline__ void nibble_bytes(const uint32_t (&v)[32], int base, 
   }
   p = __byte_perm(t[0], t[1], 0x6420) & P2<T>::kByteMask;  // bytes: elements 0, 1, 2, 3
   q = __byte_perm(t[2], t[3], 0x6420) & P2<T>::kByteMask;  // bytes: elements 4, 5, 6, 7
+}
+// the same from 4 packed pairs of already rounded z values (elements base .. base+7 of a row held as pairs)
+template <typename T>
+__device__ __forceinline__ void nibble_bytes_packed(const uint32_t* zz, float s, float inv_s, uint32_t& p, uint32_t& q) {
+  uint32_t t[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) t[i] = P2<T>::nibbles(P2<T>::quot(P2<T>::lo(zz[i]), P2<T>::hi(zz[i]), s, inv_s));
+  p = __byte_perm(t[0], t[1], 0x6420) & P2<T>::kByteMask;
+  q = __byte_perm(t[2], t[3], 0x6420) & P2<T>::kByteMask;
 }
 // 8 nibble-bytes -> one packed word, nibble i at bits 4i
 __device__ __forceinline__ uint32_t pack8(uint32_t p, uint32_t q) {

@@ -254,17 +254,25 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       tc_fence_before();
       mbar_arrive(smem_u32(&misc->d2_empty[e]));  // the Z accumulators of this stage are free again
 
+      // round Z to the activation dtype once, as packed pairs; both passes work on the pairs
+      uint32_t zz[32];
       float s = 1.f, inv_s = 1.f;
       if (MODE != kTransform) {
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;  // four chains keep the dependent-latency short
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          a0 = fmaxf(a0, fabsf(__uint_as_float(v0[i])));
-          a1 = fmaxf(a1, fabsf(__uint_as_float(v0[i + 1])));
-          a2 = fmaxf(a2, fabsf(__uint_as_float(v1[i])));
-          a3 = fmaxf(a3, fabsf(__uint_as_float(v1[i + 1])));
+        for (int i = 0; i < 16; ++i) {
+          zz[i] = P2<T>::cvt(__uint_as_float(v0[2 * i]), __uint_as_float(v0[2 * i + 1]));
+          zz[16 + i] = P2<T>::cvt(__uint_as_float(v1[2 * i]), __uint_as_float(v1[2 * i + 1]));
         }
-        float amax = valid ? fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)) : 0.f;
+        uint32_t m0 = zz[0], m1 = zz[1], m2 = zz[2], m3 = zz[3];  // four chains keep the dependent latency short
+#pragma unroll
+        for (int i = 4; i < 32; i += 4) {
+          m0 = P2<T>::absmax(m0, zz[i]);
+          m1 = P2<T>::absmax(m1, zz[i + 1]);
+          m2 = P2<T>::absmax(m2, zz[i + 2]);
+          m3 = P2<T>::absmax(m3, zz[i + 3]);
+        }
+        m0 = P2<T>::absmax(P2<T>::absmax(m0, m1), P2<T>::absmax(m2, m3));
+        float amax = valid ? fmaxf(fabsf(P2<T>::lo(m0)), fabsf(P2<T>::hi(m0))) : 0.f;
         if (warp_uniform) {
 #pragma unroll
           for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -281,7 +289,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
         // max of the rounded values = rounded max; clip * absmax and the division by 7 are rounded like the reference.
         // top / 7 can neither hit nor come within 2^-13 (relative) of a midpoint of the 16-bit format, so the
         // float32 product with 1/7 rounds to the same 16-bit value as the exact quotient.
-        const float top = DT<T>::rnd(DT<T>::rnd(amax) * clip);
+        const float top = DT<T>::rnd(amax * clip);  // amax already is a value of the activation dtype
         s = fmaxf(DT<T>::rnd(top * 0.142857149f), DT<T>::floor_scale());
         inv_s = __frcp_rn(s);
         if (valid && mi == 0) store_scale(scales, tok, s, scale_dtype);
@@ -304,7 +312,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
           uint32_t pb[4], qb[4];
           if (!zero_scale) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) nibble_bytes<T>(v, 8 * j, s, inv_s, pb[j], qb[j]);
+            for (int j = 0; j < 4; ++j) nibble_bytes_packed<T>(&zz[half * 16 + 4 * j], s, inv_s, pb[j], qb[j]);
           } else {
             // the reference divides by zero here: +-inf clamps to 7 / -8, 0/0 counts as 0
 #pragma unroll
@@ -312,7 +320,8 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
               pb[j] = qb[j] = 0;
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
-                const float z0 = DT<T>::rnd(__uint_as_float(v[8 * j + i])), z1 = DT<T>::rnd(__uint_as_float(v[8 * j + 4 + i]));
+                const uint32_t pz = zz[half * 16 + 4 * j + (i >> 1)], qz = zz[half * 16 + 4 * j + 2 + (i >> 1)];
+                const float z0 = (i & 1) ? P2<T>::hi(pz) : P2<T>::lo(pz), z1 = (i & 1) ? P2<T>::hi(qz) : P2<T>::lo(qz);
                 pb[j] |= (uint32_t)(z0 > 0.f ? 15 : (z0 < 0.f ? 0 : 8)) << (8 * i);
                 qb[j] |= (uint32_t)(z1 > 0.f ? 15 : (z1 < 0.f ? 0 : 8)) << (8 * i);
               }

@@ -32,28 +32,21 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// Bounded wait: gives up after `limit_cycles` SM clocks and returns false (the caller records the failure and
-// leaves); a healthy pipeline never gets near the limit.  The retries pass a suspend-time hint, so a waiting thread
-// is parked by the hardware until the phase completes instead of competing for issue slots with the warp that
-// feeds the tensor core.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, long long limit_cycles = 4000000000LL) {
+// Bounded wait: gives up after `limit_polls` unsuccessful polls and returns false (the caller records the failure
+// and leaves); a healthy pipeline never gets near the limit.  Each poll is a try_wait with a suspend-time hint, so
+// the hardware may park the thread until the phase completes; the loop itself is three instructions, which keeps
+// waiting warps from eating the issue slots and ALU cycles of the warps that do the work.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit_polls = 1u << 26) {
   uint32_t ok = 0;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}\n"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  if (ok) return true;
-  const long long t0 = clock64();
-  while (true) {
+  for (uint32_t polls = 0; polls < limit_polls; ++polls) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}\n"
-        : "=r"(ok) : "r"(bar), "r"(parity), "r"(200000u) : "memory");
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(100000u) : "memory");
     if (ok) return true;
-    if (clock64() - t0 > limit_cycles) return false;
   }
+  return false;
 }
 
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
