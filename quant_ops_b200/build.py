@@ -48,7 +48,7 @@ def build_lib(verbose: bool = False, force: bool = False) -> str:
         obj = os.path.join(OBJ, src.replace(".cu", ".o"))
         path = os.path.join(CSRC, src)
         if force or _stale(obj, [path, __file__] + headers):
-            cmd = [nvcc, *NVCC_FLAGS, "-c", path, "-o", obj]
+            cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("QO_NVCC_EXTRA", "").split(), "-c", path, "-o", obj]
             res = subprocess.run(cmd, capture_output=True, text=True)
             with open(obj + ".log", "w") as fh:
                 fh.write(" ".join(cmd) + "\n" + res.stdout + res.stderr)

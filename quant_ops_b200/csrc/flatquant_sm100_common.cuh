@@ -62,6 +62,13 @@ template <> struct P2<__nv_bfloat16> {
     return d;
   }
   static __device__ __forceinline__ uint32_t quot(float z0, float z1, float, float inv_s) { return cvt(z0 * inv_s, z1 * inv_s); }
+  // nibbles() without the clamp, for rows whose quotients cannot leave (-7.5, 7.5)
+  static __device__ __forceinline__ uint32_t nibbles_inrange(uint32_t q) {
+    uint32_t d;
+    asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(q), "r"(0x43484348u));
+    return d;
+  }
+  static constexpr uint32_t kFold = 0x44u;  // see fold_pair
 };
 template <> struct P2<__half> {
   static __device__ __forceinline__ uint32_t absmax(uint32_t a, uint32_t b) {
@@ -92,6 +99,12 @@ template <> struct P2<__half> {
     q1 = fmaf(fmaf(-q1, s, z1), inv_s, q1);
     return cvt(q0, q1);
   }
+  static __device__ __forceinline__ uint32_t nibbles_inrange(uint32_t q) {
+    uint32_t d;
+    asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(q), "r"(0x64086408u));
+    return d;
+  }
+  static constexpr uint32_t kFold = 0x06u;
 };
 
 // 32 accumulator values of one row -> 32 offset-binary nibbles, as 4 words of 4 bytes-with-a-nibble each pair
@@ -115,6 +128,31 @@ __device__ __forceinline__ void nibble_bytes_packed(const uint32_t* zz, float s,
   for (int i = 0; i < 4; ++i) t[i] = P2<T>::nibbles(P2<T>::quot(P2<T>::lo(zz[i]), P2<T>::hi(zz[i]), s, inv_s));
   p = __byte_perm(t[0], t[1], 0x6420) & P2<T>::kByteMask;
   q = __byte_perm(t[2], t[3], 0x6420) & P2<T>::kByteMask;
+}
+// One word out of nibbles(): both halves are C + n with the nibble n in the low 4 bits.  Returns a word whose LOW
+// BYTE is n_lo + 16 * n_hi: subtracting kFold from the low half makes the constant bits that the shift by 12 folds
+// in cancel modulo 256.  Two integer multiply-adds, which run on the FMA pipe rather than the busier ALU pipe.
+template <typename T>
+__device__ __forceinline__ uint32_t fold_pair(uint32_t t) {
+  uint32_t a, u;
+  asm("mad.lo.u32 %0, %1, 1, %2;" : "=r"(a) : "r"(t), "r"(0u - P2<T>::kFold));
+  asm("mad.hi.u32 %0, %1, %2, %1;" : "=r"(u) : "r"(a), "r"(1u << 20));  // (a >> 12) + a
+  return u;
+}
+// four folded pairs -> the packed word of 8 nibbles
+__device__ __forceinline__ uint32_t gather4(uint32_t u0, uint32_t u1, uint32_t u2, uint32_t u3) {
+  return __byte_perm(__byte_perm(u0, u1, 0x0040), __byte_perm(u2, u3, 0x0040), 0x5410);
+}
+// 8 rounded z values held as 4 packed pairs -> packed word; CLAMP = false only when |z / s| < 7.5 is known
+template <typename T, bool CLAMP>
+__device__ __forceinline__ uint32_t quantize8(const uint32_t* zz, float s, float inv_s) {
+  uint32_t u[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t q = P2<T>::quot(P2<T>::lo(zz[i]), P2<T>::hi(zz[i]), s, inv_s);
+    u[i] = fold_pair<T>(CLAMP ? P2<T>::nibbles(q) : P2<T>::nibbles_inrange(q));
+  }
+  return gather4(u[0], u[1], u[2], u[3]);
 }
 // 8 nibble-bytes -> one packed word, nibble i at bits 4i
 __device__ __forceinline__ uint32_t pack8(uint32_t p, uint32_t q) {

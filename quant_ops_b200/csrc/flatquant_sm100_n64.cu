@@ -26,6 +26,14 @@ namespace {
 using namespace ptx;
 using namespace fq;
 
+// Pipeline tracing for development builds (-DQO_TRACE): CTA 0 records clock64() at role hand-offs.
+#ifdef QO_TRACE
+__device__ long long* g_trace = nullptr;
+#define TR(role, it, ev) do { if (g_trace && blockIdx.x == 0 && (it) < 16) g_trace[((role) * 16 + (it)) * 8 + (ev)] = clock64(); } while (0)
+#else
+#define TR(role, it, ev) do { } while (0)
+#endif
+
 constexpr int kThreads = 480;                  // 15 warps: TMA, first-product issuer, 4 + 4 + 4 epilogue, second-product issuer
 constexpr int kGroup = 2;                      // tokens per group
 constexpr int kXStages = 6;
@@ -151,6 +159,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       long long grp = blockIdx.x;
       for (int it = 0; it < mine; ++it, grp += gridDim.x) {
         if (!mbar_wait(smem_u32(&misc->empty_x[s]), ph ^ 1)) { atomicCAS(status, 0u, 0x600u + s); break; }
+        TR(0, it, 0);
         const uint32_t bar = smem_u32(&misc->full_x[s]);
         mbar_arrive_expect_tx(bar, bytes);
         tma_load_3d(smem_base + kOffX + s * kStageBytes, &x_map, bar, 0, 0, (int)(grp * kGroup));
@@ -167,13 +176,16 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       int sx = 0, phx = 0, s1 = 0, ph1 = 0;
       for (int it = 0; it < mine; ++it) {
         if (!mbar_wait(smem_u32(&misc->full_x[sx]), phx)) { atomicCAS(status, 0u, 0x610u + sx); break; }
+        TR(1, it, 0);
         if (!mbar_wait(smem_u32(&misc->d1_empty[s1]), ph1 ^ 1)) { atomicCAS(status, 0u, 0x620u + s1); break; }
         tc_fence_after();
+        TR(1, it, 1);
         const uint64_t da = desc_x0 + (uint64_t)(sx * (kStageBytes >> 4));
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) mma_f16_ss(tmem + s1 * 64, da + ks * 2, desc_r + ks * 2, idesc1, ks);
         mma_commit(smem_u32(&misc->empty_x[sx]));
         mma_commit(smem_u32(&misc->d1_full[s1]));
+        TR(1, it, 2);
         if (++sx == kXStages) { sx = 0; phx ^= 1; }
         if (++s1 == kYStages) { s1 = 0; ph1 ^= 1; }
       }
@@ -189,13 +201,16 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       for (int it = 0; it < mine; ++it) {
         const int e = it & 1, ph = (it >> 1) & 1;
         if (!mbar_wait(smem_u32(&misc->y_full[sy]), phy)) { atomicCAS(status, 0u, 0x630u + sy); break; }
+        TR(2, it, 0);
         if (!mbar_wait(smem_u32(&misc->d2_empty[e]), ph ^ 1)) { atomicCAS(status, 0u, 0x640u + e); break; }
         tc_fence_after();
+        TR(2, it, 1);
         uint64_t da2 = desc_ll, db2 = desc_y0 + (uint64_t)(sy * (kStageBytes >> 4));
 #pragma unroll 1
         for (int ks = 0; ks < ksteps2; ++ks, da2 += 2, db2 += 128) mma_f16_ss(tmem + kColZ + e * 128, da2, db2, idesc2, ks);
         mma_commit(smem_u32(&misc->y_empty[sy]));
         mma_commit(smem_u32(&misc->d2_full[e]));
+        TR(2, it, 2);
         if (++sy == kYStages) { sy = 0; phy ^= 1; }
       }
     }
@@ -207,6 +222,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&misc->d1_full[s]), ph))) { atomicCAS(status, 0u, 0x700u + s); break; }
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&misc->y_empty[s]), ph ^ 1))) { atomicCAS(status, 0u, 0x710u + s); break; }
       tc_fence_after();
+      if (tid == 64) TR(3, it, 0);
       uint32_t v0[32], v1[32];
       const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + s * 64;
       tmem_ld_32x32b_x32(taddr, v0);
@@ -214,6 +230,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(smem_u32(&misc->d1_empty[s]));  // accumulators are in registers: the stage can be overwritten
+      if (tid == 64) TR(3, it, 1);
       if (r < rows_group) {
         uint8_t* yrow = smem + kOffY + s * kStageBytes + r * 128;
 #pragma unroll
@@ -230,6 +247,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       }
       fence_proxy_async_smem();
       mbar_arrive(smem_u32(&misc->y_full[s]));
+      if (tid == 64) TR(3, it, 2);
       if (++s == kYStages) { s = 0; ph ^= 1; }
     }
   } else {
@@ -244,6 +262,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       const int ph = use & 1, buf = use % 3;
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&misc->d2_full[e]), ph))) { atomicCAS(status, 0u, 0x800u + e); break; }
       tc_fence_after();
+      if (lane == 0 && q == 2) TR(4 + e, use, 0);
       const long long tok = grp * kGroup + c;
       const bool valid = active && tok < tokens;
       const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + kColZ + e * 128 + (active ? c : 0) * 64;
@@ -253,10 +272,12 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(smem_u32(&misc->d2_empty[e]));  // the Z accumulators of this stage are free again
+      if (lane == 0 && q == 2) TR(4 + e, use, 1);
 
       // round Z to the activation dtype once, as packed pairs; both passes work on the pairs
       uint32_t zz[32];
       float s = 1.f, inv_s = 1.f;
+      bool clamp_needed = true;
       if (MODE != kTransform) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -273,9 +294,9 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
         }
         m0 = P2<T>::absmax(P2<T>::absmax(m0, m1), P2<T>::absmax(m2, m3));
         float amax = valid ? fmaxf(fabsf(P2<T>::lo(m0)), fabsf(P2<T>::hi(m0))) : 0.f;
+        const float row_amax = amax;  // this row's own extreme, used below to skip the clamp
         if (warp_uniform) {
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+          amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(amax)));  // non-negative floats order as integers
           if (lane == 0 && active) atomicMax(&misc->absmax_bits[e][buf][c], __float_as_int(amax));
         } else if (active) {
           atomicMax(&misc->absmax_bits[e][buf][c], __float_as_int(amax));
@@ -284,6 +305,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
         const uint32_t gs = smem_u32(&misc->set_sync[e]);
         mbar_arrive(gs);
         if (!__all_sync(0xffffffffu, mbar_wait(gs, ph))) { atomicCAS(status, 0u, 0x810u + e); break; }
+        if (lane == 0 && q == 2) TR(4 + e, use, 2);
         if (active) amax = __int_as_float(misc->absmax_bits[e][buf][c]);
         if (l < 8) misc->absmax_bits[e][(use + 2) % 3][l] = 0;
         // max of the rounded values = rounded max; clip * absmax and the division by 7 are rounded like the reference.
@@ -293,8 +315,11 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
         s = fmaxf(DT<T>::rnd(top * 0.142857149f), DT<T>::floor_scale());
         inv_s = __frcp_rn(s);
         if (valid && mi == 0) store_scale(scales, tok, s, scale_dtype);
+        // a quotient can only leave [-8, 7] after rounding if some |z| / s reaches 7.5; most warps have no such row
+        clamp_needed = __any_sync(0xffffffffu, !(row_amax * inv_s < 7.4f));
       }
       const bool zero_scale = (MODE != kTransform) && (s == 0.f);
+      if (lane == 0 && q == 2) TR(4 + e, use, 3);
 
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
@@ -307,6 +332,19 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
             for (int j = 0; j < 8; ++j)
               dst[j] = make_float4(DT<T>::rnd(__uint_as_float(v[4 * j])), DT<T>::rnd(__uint_as_float(v[4 * j + 1])),
                                    DT<T>::rnd(__uint_as_float(v[4 * j + 2])), DT<T>::rnd(__uint_as_float(v[4 * j + 3])));
+          }
+        } else if (MODE == kPacked && !zero_scale) {
+          uint32_t w[4];
+          if (clamp_needed) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) w[j] = quantize8<T, true>(&zz[half * 16 + 4 * j], s, inv_s);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) w[j] = quantize8<T, false>(&zz[half * 16 + 4 * j], s, inv_s);
+          }
+          if (valid) {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(out) + tok * (feat / 8) + (mi * 64 + c0) / 8);
+            *dst = make_uint4(w[0], w[1], w[2], w[3]);
           }
         } else {
           uint32_t pb[4], qb[4];
@@ -339,6 +377,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
           }
         }
       }
+      if (lane == 0 && q == 2) TR(4 + e, use, 4);
     }
   }
 
@@ -380,6 +419,12 @@ int launch_mode(int mode, const CUtensorMap& map, const void* left, const void* 
 }
 
 }  // namespace
+
+#ifdef QO_TRACE
+extern "C" __attribute__((visibility("default"))) int qo_debug_set_trace(long long* p) {
+  return (int)cudaMemcpyToSymbol(g_trace, &p, sizeof p);
+}
+#endif
 
 bool flatquant_sm100_n64_supported(int m, int n) { return n == 64 && m >= 16 && m <= 64 && (m % 16) == 0; }
 

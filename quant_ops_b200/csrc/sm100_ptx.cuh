@@ -45,6 +45,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
         "selp.u32 %0, 1, 0, p;\n\t}\n"
         : "=r"(ok) : "r"(bar), "r"(parity), "r"(100000u) : "memory");
     if (ok) return true;
+    if (polls > 4) __nanosleep(polls > 64 ? 256 : 32);
   }
   return false;
 }
