@@ -154,6 +154,9 @@ __device__ __forceinline__ uint32_t quantize8(const uint32_t* zz, float s, float
   }
   return gather4(u[0], u[1], u[2], u[3]);
 }
+// round one float to the activation dtype through the packed convert (ALU pipe, short latency)
+template <typename T>
+__device__ __forceinline__ float rnd1(float x) { return P2<T>::lo(P2<T>::cvt(x, x)); }
 // 8 nibble-bytes -> one packed word, nibble i at bits 4i
 __device__ __forceinline__ uint32_t pack8(uint32_t p, uint32_t q) {
   p |= p >> 4;

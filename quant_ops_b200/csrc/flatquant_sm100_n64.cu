@@ -1,20 +1,25 @@
 // FlatQuant quantizer for sm_100a, right transform of size 64 (features = M x 64 with M in {16, 32, 48, 64}):
 // the activation-scale configuration (4096 = 64 x 64) runs here.
 //
-// A tcgen05.mma costs about the same for N = 64 as for N = 256, so the work is shaped into few, wide instructions.
-// One persistent CTA per SM works on groups of 4 tokens:
+// One persistent CTA per SM works on groups of 2 tokens (2M <= 128 rows of 64 elements):
 //
-//   warp 0      TMA: 3-D tensor map (n, m, token), box 64 x M x 4 -> 4M rows of 128 bytes, 128-byte swizzle
-//   warp 1      MMA issuer
-//                 Y  = X . R      per 128-row slice of the group: A = X rows (K-major), B = R^T (K-major), N = 64
-//                 Z  = LL . Y4    once per group: A = LL = floor(128/M) copies of L^T stacked (K-major),
-//                                 B = the 4 tokens' Y side by side along N (N-major, N = 256), K = M
-//   warps 2-5   Y pass: tensor memory -> round to the activation dtype -> shared memory in the B layout
-//   warps 6-13  quantize pass: lane block c of group e owns token e*copies + c of the group; thread = one row of that
-//               token: absmax (shared-memory atomics per token), scale, int4 codes, 16-byte stores
+//   warp 0       TMA: 3-D tensor map (n, m, token), box 64 x M x 2 -> 2M rows of 128 bytes, 128-byte swizzle, 6 stages
+//   warp 1       issues Y = X . R        A = X rows (K-major), B = R^T (K-major), M = 128, N = 64, K = 64
+//   warp 2       issues Z = LL . Y2      A = LL = floor(128/M) copies of L^T stacked (K-major),
+//                                        B = the 2 tokens' Y side by side along N (N-major, N = 128), K = M
+//   warps 3-10   Y pass: tensor memory -> round to the activation dtype -> shared memory in the B layout;
+//                warp (q, h) handles columns 32h..32h+31 of tensor-memory lanes 32q..32q+31
+//   warps 11-26  quantize pass, two sets of 8 warps that alternate between groups; lane block c of a set holds a copy
+//                of the Z rows and serves token c; a thread rounds its 32 values once (packed pairs), the token's
+//                absmax is combined through shared memory, then scale, int4 codes and one 16-byte store
 //
 // Stacking copies of L^T makes every copy's lanes hold the same Z rows, so different lane blocks can serve
-// different tokens and all 256 quantize threads have work.  No block-diagonal padding is multiplied.
+// different tokens and nothing is multiplied by block-diagonal padding.  The accumulator stages are released as
+// soon as their values sit in registers.  What the cycle counters showed while shaping this kernel: a try_wait
+// costs about 170 cycles even on a completed phase (two barriers are therefore polled together), an mbarrier
+// arrival is an atomic on one word (one arrival per warp, not per thread), a tcgen05.mma costs about the same for
+// N = 64 as for N = 128, and integer / conversion work runs on the half-rate ALU pipe (the nibble packing uses
+// integer multiply-adds instead).
 //
 // Rounding points and the exactness arguments are those of flatquant_sm100.cu (reference:
 // src/quant_ops/ops/quantization/flatquant/ops.py:99-117).  Every mbarrier wait is bounded.
@@ -34,7 +39,8 @@ __device__ long long* g_trace = nullptr;
 #define TR(role, it, ev) do { } while (0)
 #endif
 
-constexpr int kThreads = 480;                  // 15 warps: TMA, first-product issuer, 4 + 4 + 4 epilogue, second-product issuer
+constexpr int kThreads = 864;                  // 27 warps: TMA, two MMA issuers, 8 (Y pass) + 2 x 8 (quantize pass)
+constexpr int kEpi1Warp0 = 3, kEpi2Warp0 = 11; // first warp of the Y pass / of the two quantize sets
 constexpr int kGroup = 2;                      // tokens per group
 constexpr int kXStages = 6;
 constexpr int kYStages = 3;                    // also the number of Y accumulator stages
@@ -76,14 +82,14 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
     for (int i = 0; i < kXStages; ++i) { mbar_init(smem_u32(&misc->full_x[i]), 1); mbar_init(smem_u32(&misc->empty_x[i]), 1); }
     for (int i = 0; i < kYStages; ++i) {
       mbar_init(smem_u32(&misc->d1_full[i]), 1);
-      mbar_init(smem_u32(&misc->d1_empty[i]), 128);
-      mbar_init(smem_u32(&misc->y_full[i]), 128);
+      mbar_init(smem_u32(&misc->d1_empty[i]), 8);  // one arrival per warp of the Y pass
+      mbar_init(smem_u32(&misc->y_full[i]), 8);
       mbar_init(smem_u32(&misc->y_empty[i]), 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&misc->d2_full[i]), 1);
-      mbar_init(smem_u32(&misc->d2_empty[i]), 128);
-      mbar_init(smem_u32(&misc->set_sync[i]), 128);
+      mbar_init(smem_u32(&misc->d2_empty[i]), 8);  // one arrival per warp of a quantize set
+      mbar_init(smem_u32(&misc->set_sync[i]), 8);
     }
     for (int i = 0; i < 2 * 3 * 8; ++i) (&misc->absmax_bits[0][0][0])[i] = 0;
     fence_barrier_init();
@@ -98,8 +104,8 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
   tc_fence_after();
   const uint32_t tmem = misc->tmem_base;
 
-  if (warp != 0 && warp != 14) {
-    constexpr int kStagers = 13 * 32;
+  if (warp != 0) {
+    constexpr int kStagers = kThreads - 32;
     const int t13 = tid - 32;
     // raw copies of L and R into the (still unused) Y stages, all 16-byte loads in flight at once
     uint16_t* raw_l = reinterpret_cast<uint16_t*>(smem + kOffY);
@@ -175,9 +181,11 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       const uint64_t desc_r = umma_smem_desc_sw128(smem_base + kOffR, 16, 1024);
       int sx = 0, phx = 0, s1 = 0, ph1 = 0;
       for (int it = 0; it < mine; ++it) {
-        if (!mbar_wait(smem_u32(&misc->full_x[sx]), phx)) { atomicCAS(status, 0u, 0x610u + sx); break; }
+        if (const int w = mbar_wait2(smem_u32(&misc->full_x[sx]), phx, smem_u32(&misc->d1_empty[s1]), ph1 ^ 1)) {
+          atomicCAS(status, 0u, 0x600u + 0x10u * w + sx);
+          break;
+        }
         TR(1, it, 0);
-        if (!mbar_wait(smem_u32(&misc->d1_empty[s1]), ph1 ^ 1)) { atomicCAS(status, 0u, 0x620u + s1); break; }
         tc_fence_after();
         TR(1, it, 1);
         const uint64_t da = desc_x0 + (uint64_t)(sx * (kStageBytes >> 4));
@@ -190,7 +198,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
         if (++s1 == kYStages) { s1 = 0; ph1 ^= 1; }
       }
     }
-  } else if (warp == 14) {
+  } else if (warp == 2) {
     // second-product issuer: its waits and commits overlap with the first-product MMAs of later groups
     if (lane == 0) {
       const uint32_t idesc2 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 0, 1, 128, 128);
@@ -200,9 +208,11 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       int sy = 0, phy = 0;
       for (int it = 0; it < mine; ++it) {
         const int e = it & 1, ph = (it >> 1) & 1;
-        if (!mbar_wait(smem_u32(&misc->y_full[sy]), phy)) { atomicCAS(status, 0u, 0x630u + sy); break; }
+        if (const int w = mbar_wait2(smem_u32(&misc->y_full[sy]), phy, smem_u32(&misc->d2_empty[e]), ph ^ 1)) {
+          atomicCAS(status, 0u, 0x620u + 0x10u * w + sy);
+          break;
+        }
         TR(2, it, 0);
-        if (!mbar_wait(smem_u32(&misc->d2_empty[e]), ph ^ 1)) { atomicCAS(status, 0u, 0x640u + e); break; }
         tc_fence_after();
         TR(2, it, 1);
         uint64_t da2 = desc_ll, db2 = desc_y0 + (uint64_t)(sy * (kStageBytes >> 4));
@@ -214,45 +224,44 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
         if (++sy == kYStages) { sy = 0; phy ^= 1; }
       }
     }
-  } else if (warp < 6) {
-    // ---- Y pass: row r of the group = tensor-memory lane r -------------------------------------------------
-    const int q = warp & 3, r = q * 32 + lane;
+  } else if (warp < kEpi2Warp0) {
+    // ---- Y pass: 8 warps; warp (q, h) converts columns 32h .. 32h+31 of tensor-memory lanes 32q .. 32q+31 ------
+    const int q = warp & 3, h = (warp - kEpi1Warp0) >> 2, r = q * 32 + lane;
     int s = 0, ph = 0;
     for (int it = 0; it < mine; ++it) {
-      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&misc->d1_full[s]), ph))) { atomicCAS(status, 0u, 0x700u + s); break; }
-      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&misc->y_empty[s]), ph ^ 1))) { atomicCAS(status, 0u, 0x710u + s); break; }
+      if (__any_sync(0xffffffffu, mbar_wait2(smem_u32(&misc->d1_full[s]), ph, smem_u32(&misc->y_empty[s]), ph ^ 1) != 0)) {
+        atomicCAS(status, 0u, 0x700u + s);
+        break;
+      }
       tc_fence_after();
-      if (tid == 64) TR(3, it, 0);
-      uint32_t v0[32], v1[32];
-      const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + s * 64;
-      tmem_ld_32x32b_x32(taddr, v0);
-      tmem_ld_32x32b_x32(taddr + 32, v1);
+      if (tid == kEpi1Warp0 * 32) TR(3, it, 0);
+      uint32_t v[32];
+      tmem_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + s * 64 + h * 32, v);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(smem_u32(&misc->d1_empty[s]));  // accumulators are in registers: the stage can be overwritten
-      if (tid == 64) TR(3, it, 1);
+      mbar_arrive_warp(smem_u32(&misc->d1_empty[s]));  // accumulators are in registers: the stage can be overwritten
+      if (tid == kEpi1Warp0 * 32) TR(3, it, 1);
       if (r < rows_group) {
         uint8_t* yrow = smem + kOffY + s * kStageBytes + r * 128;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t* v = j < 4 ? v0 : v1;
-          const int b = (j & 3) * 8;
+        for (int j = 0; j < 4; ++j) {
           uint4 w;
-          w.x = pack2<T>(__uint_as_float(v[b + 0]), __uint_as_float(v[b + 1]));
-          w.y = pack2<T>(__uint_as_float(v[b + 2]), __uint_as_float(v[b + 3]));
-          w.z = pack2<T>(__uint_as_float(v[b + 4]), __uint_as_float(v[b + 5]));
-          w.w = pack2<T>(__uint_as_float(v[b + 6]), __uint_as_float(v[b + 7]));
-          *reinterpret_cast<uint4*>(yrow + ((j ^ (r & 7)) << 4)) = w;
+          w.x = pack2<T>(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+          w.y = pack2<T>(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+          w.z = pack2<T>(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+          w.w = pack2<T>(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+          *reinterpret_cast<uint4*>(yrow + (((h * 4 + j) ^ (r & 7)) << 4)) = w;
         }
       }
       fence_proxy_async_smem();
-      mbar_arrive(smem_u32(&misc->y_full[s]));
-      if (tid == 64) TR(3, it, 2);
+      mbar_arrive_warp(smem_u32(&misc->y_full[s]));
+      if (tid == kEpi1Warp0 * 32) TR(3, it, 2);
       if (++s == kYStages) { s = 0; ph ^= 1; }
     }
   } else {
-    // ---- quantize pass: set e (4 warps) takes the groups with (it & 1) == e ----------------------------------
-    const int e = (warp - 6) >> 2, q = warp & 3, l = q * 32 + lane;
+    // ---- quantize pass ---------------------------------------------------------------------------------------
+    // set e (8 warps) takes the groups with (it & 1) == e; warp (q, h) of a set works on columns 32h .. 32h+31 of lanes 32q ..
+    const int e = (warp - kEpi2Warp0) >> 3, q = warp & 3, h = ((warp - kEpi2Warp0) >> 2) & 1, l = q * 32 + lane;
     const int c = l / m, mi = l - c * m;            // lane block c holds a copy of the Z rows: it serves token c
     const bool active = c < kGroup;
     const bool warp_uniform = (m & 31) == 0;
@@ -262,31 +271,27 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       const int ph = use & 1, buf = use % 3;
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&misc->d2_full[e]), ph))) { atomicCAS(status, 0u, 0x800u + e); break; }
       tc_fence_after();
-      if (lane == 0 && q == 2) TR(4 + e, use, 0);
+      if (lane == 0 && q == 2 && h == 0) TR(4 + e, use, 0);
       const long long tok = grp * kGroup + c;
       const bool valid = active && tok < tokens;
       const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + kColZ + e * 128 + (active ? c : 0) * 64;
-      uint32_t v0[32], v1[32];
-      tmem_ld_32x32b_x32(taddr, v0);
-      tmem_ld_32x32b_x32(taddr + 32, v1);
+      uint32_t v[32];
+      tmem_ld_32x32b_x32(taddr + h * 32, v);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(smem_u32(&misc->d2_empty[e]));  // the Z accumulators of this stage are free again
-      if (lane == 0 && q == 2) TR(4 + e, use, 1);
+      mbar_arrive_warp(smem_u32(&misc->d2_empty[e]));  // the Z accumulators of this stage are free again
+      if (lane == 0 && q == 2 && h == 0) TR(4 + e, use, 1);
 
       // round Z to the activation dtype once, as packed pairs; both passes work on the pairs
-      uint32_t zz[32];
+      uint32_t zz[16];
       float s = 1.f, inv_s = 1.f;
       bool clamp_needed = true;
       if (MODE != kTransform) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          zz[i] = P2<T>::cvt(__uint_as_float(v0[2 * i]), __uint_as_float(v0[2 * i + 1]));
-          zz[16 + i] = P2<T>::cvt(__uint_as_float(v1[2 * i]), __uint_as_float(v1[2 * i + 1]));
-        }
+        for (int i = 0; i < 16; ++i) zz[i] = P2<T>::cvt(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
         uint32_t m0 = zz[0], m1 = zz[1], m2 = zz[2], m3 = zz[3];  // four chains keep the dependent latency short
 #pragma unroll
-        for (int i = 4; i < 32; i += 4) {
+        for (int i = 4; i < 16; i += 4) {
           m0 = P2<T>::absmax(m0, zz[i]);
           m1 = P2<T>::absmax(m1, zz[i + 1]);
           m2 = P2<T>::absmax(m2, zz[i + 2]);
@@ -303,28 +308,26 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
         }
         // the 128 threads of the set meet here (bounded); afterwards the slot holds the token's absmax
         const uint32_t gs = smem_u32(&misc->set_sync[e]);
-        mbar_arrive(gs);
+        mbar_arrive_warp(gs);
         if (!__all_sync(0xffffffffu, mbar_wait(gs, ph))) { atomicCAS(status, 0u, 0x810u + e); break; }
-        if (lane == 0 && q == 2) TR(4 + e, use, 2);
+        if (lane == 0 && q == 2 && h == 0) TR(4 + e, use, 2);
         if (active) amax = __int_as_float(misc->absmax_bits[e][buf][c]);
         if (l < 8) misc->absmax_bits[e][(use + 2) % 3][l] = 0;
         // max of the rounded values = rounded max; clip * absmax and the division by 7 are rounded like the reference.
         // top / 7 can neither hit nor come within 2^-13 (relative) of a midpoint of the 16-bit format, so the
         // float32 product with 1/7 rounds to the same 16-bit value as the exact quotient.
-        const float top = DT<T>::rnd(amax * clip);  // amax already is a value of the activation dtype
-        s = fmaxf(DT<T>::rnd(top * 0.142857149f), DT<T>::floor_scale());
+        const float top = rnd1<T>(amax * clip);  // amax already is a value of the activation dtype
+        s = fmaxf(rnd1<T>(top * 0.142857149f), DT<T>::floor_scale());
         inv_s = __frcp_rn(s);
-        if (valid && mi == 0) store_scale(scales, tok, s, scale_dtype);
+        if (valid && mi == 0 && h == 0) store_scale(scales, tok, s, scale_dtype);
         // a quotient can only leave [-8, 7] after rounding if some |z| / s reaches 7.5; most warps have no such row
         clamp_needed = __any_sync(0xffffffffu, !(row_amax * inv_s < 7.4f));
       }
       const bool zero_scale = (MODE != kTransform) && (s == 0.f);
-      if (lane == 0 && q == 2) TR(4 + e, use, 3);
+      if (lane == 0 && q == 2 && h == 0) TR(4 + e, use, 3);
 
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t(&v)[32] = half ? v1 : v0;
-        const int c0 = half * 32;
+      {
+        const int c0 = h * 32;
         if (MODE == kTransform) {
           if (valid) {
             float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + tok * feat + mi * 64 + c0);
@@ -337,10 +340,10 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
           uint32_t w[4];
           if (clamp_needed) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) w[j] = quantize8<T, true>(&zz[half * 16 + 4 * j], s, inv_s);
+            for (int j = 0; j < 4; ++j) w[j] = quantize8<T, true>(&zz[4 * j], s, inv_s);
           } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) w[j] = quantize8<T, false>(&zz[half * 16 + 4 * j], s, inv_s);
+            for (int j = 0; j < 4; ++j) w[j] = quantize8<T, false>(&zz[4 * j], s, inv_s);
           }
           if (valid) {
             uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(out) + tok * (feat / 8) + (mi * 64 + c0) / 8);
@@ -350,7 +353,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
           uint32_t pb[4], qb[4];
           if (!zero_scale) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) nibble_bytes_packed<T>(&zz[half * 16 + 4 * j], s, inv_s, pb[j], qb[j]);
+            for (int j = 0; j < 4; ++j) nibble_bytes_packed<T>(&zz[4 * j], s, inv_s, pb[j], qb[j]);
           } else {
             // the reference divides by zero here: +-inf clamps to 7 / -8, 0/0 counts as 0
 #pragma unroll
@@ -358,7 +361,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
               pb[j] = qb[j] = 0;
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
-                const uint32_t pz = zz[half * 16 + 4 * j + (i >> 1)], qz = zz[half * 16 + 4 * j + 2 + (i >> 1)];
+                const uint32_t pz = zz[4 * j + (i >> 1)], qz = zz[4 * j + 2 + (i >> 1)];
                 const float z0 = (i & 1) ? P2<T>::hi(pz) : P2<T>::lo(pz), z1 = (i & 1) ? P2<T>::hi(qz) : P2<T>::lo(qz);
                 pb[j] |= (uint32_t)(z0 > 0.f ? 15 : (z0 < 0.f ? 0 : 8)) << (8 * i);
                 qb[j] |= (uint32_t)(z1 > 0.f ? 15 : (z1 < 0.f ? 0 : 8)) << (8 * i);
@@ -377,7 +380,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
           }
         }
       }
-      if (lane == 0 && q == 2) TR(4 + e, use, 4);
+      if (lane == 0 && q == 2 && h == 0) TR(4 + e, use, 4);
     }
   }
 
