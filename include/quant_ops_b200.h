@@ -134,6 +134,28 @@ QO_API int qo_int4_matmul(const int32_t* a, int64_t lda, const int32_t* b, int64
                           void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * qo_int4_matmul without any allocation.  It has no counterpart in the reference.
+ *
+ * For hosts that cannot let a library allocate device memory: a serving process that gave all of the GPU's memory
+ * to its own pool at start-up has none left for a late cudaMalloc, and a cudaMalloc inside a serving step would
+ * synchronise the device.  The scratch for the widened operands lives in a device array inside the library, so the
+ * call allocates nothing (no cudaMalloc, no cudaFree, no allocating library routine), and every GPU that loads the
+ * library holds qo_int4_matmul_static_max_bytes() (8 MiB) until the process exits.
+ *
+ * Limits and rules:
+ *   - tokens*k + n_out*k bytes (each rounded up to 256) must not exceed qo_int4_matmul_static_max_bytes(); larger
+ *     problems return QO_ERR_WORKSPACE.  Only the shapes of the tcgen05 kernel are served (k % 16 == 0,
+ *     n_out % 8 == 0, b with unit stride along k or along n_out); others return QO_ERR_UNSUPPORTED.
+ *   - the first call on a device looks up the array's device address; make it before any stream capture.
+ *   - all calls share the one array: calls that may overlap on the GPU (different streams) race; serialise them.
+ *   - same arithmetic and same results as qo_int4_matmul (fp16 or bf16 output, no accumulator dump, no bias).
+ */
+QO_API size_t qo_int4_matmul_static_max_bytes(void);
+QO_API int qo_int4_matmul_static(const int32_t* a, int64_t lda, const int32_t* b, int64_t b_stride_k,
+                                 int64_t b_stride_n, const float* scale_a, const float* scale_b, void* out,
+                                 int out_dtype, int64_t tokens, int64_t k, int64_t n_out, void* stream);
+
+/*
  * Fused W4A4 linear layer: quantize activations (as qo_flatquant_quantize with packing) and multiply by
  * packed weights w [n_out, m*n/8] (K contiguous) with per-output-channel scales.
  * Stands in for the composition a user of the reference writes,

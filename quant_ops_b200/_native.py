@@ -31,6 +31,8 @@ PROTOTYPES = {
     "qo_dequantize_int4": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _int, _vp]),
     "qo_int4_matmul_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "qo_int4_matmul": (_int, [_vp, _i64, _vp, _i64, _i64, _vp, _vp, _vp, _int, _i64, _i64, _i64, _vp, _vp, _sz, _vp]),
+    "qo_int4_matmul_static_max_bytes": (_sz, []),
+    "qo_int4_matmul_static": (_int, [_vp, _i64, _vp, _i64, _i64, _vp, _vp, _vp, _int, _i64, _i64, _i64, _vp]),
     "qo_w4a4_linear_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "qo_w4a4_linear": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _int, _int, _i64, _f32, _int, _int, _vp, _sz, _vp]),
     "qo_pack_int4": (_int, [_vp, _vp, _i64, _i64, _vp]),

@@ -367,4 +367,23 @@ int launch_gemm_sm100(const int32_t* a, int64_t lda, const int32_t* b, int64_t b
   return launch_gemm_sm100_s8(a8, b8, sa, sb, out, out_dtype, t, k, n, acc_out, bias, stream);
 }
 
+// ---- pieces for callers that bring their own scratch and status word (int4_gemm_static.cu) ------------------------
+int launch_widen_b(const int32_t* b, int64_t bsk, int64_t bsn, int8_t* b8, int64_t n, int64_t k, cudaStream_t stream) {
+  if (bsk == 1) return launch_widen_rows(b, bsn, b8, n, k, stream);
+  dim3 grid((unsigned)((n + 31) / 32), (unsigned)((k / 8 + 31) / 32));
+  widen_transpose_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const uint32_t*>(b), bsk, bsn,
+                                                   reinterpret_cast<uint2*>(b8), n, k / 8);
+  return check_launch("widen_transpose_kernel");
+}
+
+int launch_gemm_sm100_s8_status(const int8_t* a8, const int8_t* b8, const float* sa, const float* sb, void* out,
+                                int out_dtype, int64_t t, int64_t k, int64_t n, int32_t* acc_out, uint32_t* status,
+                                cudaStream_t stream) {
+  if (reinterpret_cast<uintptr_t>(a8) % 16 || reinterpret_cast<uintptr_t>(b8) % 16 || reinterpret_cast<uintptr_t>(out) % 16 ||
+      (acc_out && reinterpret_cast<uintptr_t>(acc_out) % 16))
+    return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: operands of the tcgen05 kernel must be 16-byte aligned");
+  if (out_dtype == QO_F16) return launch_gemm_typed<__half>(a8, b8, sa, sb, out, acc_out, nullptr, t, k, n, status, stream);
+  return launch_gemm_typed<__nv_bfloat16>(a8, b8, sa, sb, out, acc_out, nullptr, t, k, n, status, stream);
+}
+
 }  // namespace qo
