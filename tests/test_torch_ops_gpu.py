@@ -69,3 +69,24 @@ def test_runs_on_a_side_stream_and_in_a_cuda_graph():
     graph.replay()
     torch.cuda.synchronize()
     assert torch.equal(gc, torch.roll(ref_c, 1, 0)) and torch.equal(gs, torch.roll(ref_s, 1, 0))
+
+
+def test_w4a4_linear_module_matches_the_two_step_path():
+    """The layer object (load-time weight packing, any leading dimensions, bias, output in the input dtype)."""
+    x, left, right = make_inputs(48, 4096, "bf16", 77, True)
+    g = torch.Generator().manual_seed(8)
+    w = torch.randn(256, 4096, generator=g) * 0.02
+    bias = (torch.randn(256, generator=g) * 0.1).bfloat16()
+    layer = q.W4A4Linear(4096, 256, bias=True, clip_ratio=0.9, dtype=torch.bfloat16, device=DEV)
+    layer.load_float(w, left.to(DEV), right.to(DEV), bias.to(DEV))
+    y = layer(x.to(DEV).view(4, 12, 4096))
+    assert y.shape == (4, 12, 256) and y.dtype == torch.bfloat16
+    codes, scales = q.flatquant_dynamic_quantize(x.to(DEV), left.to(DEV), right.to(DEV), 0.9, True)
+    ref = q.int4_matmul_ex(codes, layer.weight_packed.t(), scales, layer.weight_scale, torch.bfloat16)
+    ref = (ref.float() + bias.to(DEV).float()).bfloat16()
+    assert torch.equal(y.view(48, 256), ref)
+    # the same weights loaded as int8 codes + scales (the reference's checkpoint layout) give the same layer
+    wq, sw = O.quantize_weights(w.numpy())
+    layer2 = q.W4A4Linear(4096, 256, bias=True, clip_ratio=0.9, dtype=torch.bfloat16, device=DEV)
+    layer2.load_quantized(torch.from_numpy(wq), torch.from_numpy(sw), left.to(DEV), right.to(DEV), bias.to(DEV))
+    assert torch.equal(layer2.weight_packed, layer.weight_packed) and torch.equal(layer2(x.to(DEV)), y.view(48, 256))
