@@ -62,6 +62,22 @@ template <> struct P2<__nv_bfloat16> {
     return d;
   }
   static __device__ __forceinline__ uint32_t quot(float z0, float z1, float, float inv_s) { return cvt(z0 * inv_s, z1 * inv_s); }
+  // 1/s as two bf16 terms (both halves of a word hold the same term): hi = round(1/s), lo = round(1/s - hi)
+  static __device__ __forceinline__ void recip2(float inv_s, uint32_t& hi2, uint32_t& lo2) {
+    hi2 = cvt(inv_s, inv_s);
+    const float rest = inv_s - lo(hi2);  // exact in float32
+    lo2 = cvt(rest, rest);
+  }
+  // round(z / s) for a packed pair with two packed instructions: fma(z, hi, round(z * lo)).  The inner rounding
+  // error and the error of hi + lo together stay below the distance from z / s to the nearest rounding boundary of
+  // the format; checked exhaustively over all 128 x 128 significand pairs of z and s (both signs), which covers
+  // every normal operand because the computation is invariant under scaling by powers of two.
+  static __device__ __forceinline__ uint32_t quotp(uint32_t zz, float, float, uint32_t hi2, uint32_t lo2) {
+    uint32_t t, d;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(t) : "r"(zz), "r"(lo2));
+    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(zz), "r"(hi2), "r"(t));
+    return d;
+  }
   // nibbles() without the clamp, for rows whose quotients cannot leave (-7.5, 7.5)
   static __device__ __forceinline__ uint32_t nibbles_inrange(uint32_t q) {
     uint32_t d;
@@ -69,6 +85,7 @@ template <> struct P2<__nv_bfloat16> {
     return d;
   }
   static constexpr uint32_t kFold = 0x44u;  // see fold_pair
+  static constexpr uint32_t kHalfBits = 0x4340u;  // a half out of nibbles() is kHalfBits + nibble (see fold_quad)
 };
 template <> struct P2<__half> {
   static __device__ __forceinline__ uint32_t absmax(uint32_t a, uint32_t b) {
@@ -99,12 +116,18 @@ template <> struct P2<__half> {
     q1 = fmaf(fmaf(-q1, s, z1), inv_s, q1);
     return cvt(q0, q1);
   }
+  static __device__ __forceinline__ void recip2(float, uint32_t& hi2, uint32_t& lo2) { hi2 = lo2 = 0; }
+  // fp16 keeps the float32 route: 1/s can leave the fp16 range
+  static __device__ __forceinline__ uint32_t quotp(uint32_t zz, float s, float inv_s, uint32_t, uint32_t) {
+    return quot(lo(zz), hi(zz), s, inv_s);
+  }
   static __device__ __forceinline__ uint32_t nibbles_inrange(uint32_t q) {
     uint32_t d;
     asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(q), "r"(0x64086408u));
     return d;
   }
   static constexpr uint32_t kFold = 0x06u;
+  static constexpr uint32_t kHalfBits = 0x6400u;
 };
 
 // 32 accumulator values of one row -> 32 offset-binary nibbles, as 4 words of 4 bytes-with-a-nibble each pair
@@ -122,10 +145,11 @@ __device__ __forceinline__ void nibble_bytes(const uint32_t (&v)[32], int base, 
 }
 // the same from 4 packed pairs of already rounded z values (elements base .. base+7 of a row held as pairs)
 template <typename T>
-__device__ __forceinline__ void nibble_bytes_packed(const uint32_t* zz, float s, float inv_s, uint32_t& p, uint32_t& q) {
+__device__ __forceinline__ void nibble_bytes_packed(const uint32_t* zz, float s, float inv_s, uint32_t hi2, uint32_t lo2,
+                                                    uint32_t& p, uint32_t& q) {
   uint32_t t[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) t[i] = P2<T>::nibbles(P2<T>::quot(P2<T>::lo(zz[i]), P2<T>::hi(zz[i]), s, inv_s));
+  for (int i = 0; i < 4; ++i) t[i] = P2<T>::nibbles(P2<T>::quotp(zz[i], s, inv_s, hi2, lo2));
   p = __byte_perm(t[0], t[1], 0x6420) & P2<T>::kByteMask;
   q = __byte_perm(t[2], t[3], 0x6420) & P2<T>::kByteMask;
 }
@@ -139,20 +163,34 @@ __device__ __forceinline__ uint32_t fold_pair(uint32_t t) {
   asm("mad.hi.u32 %0, %1, %2, %1;" : "=r"(u) : "r"(a), "r"(1u << 20));  // (a >> 12) + a
   return u;
 }
+// Two words out of nibbles() (elements 0,1 and 2,3) -> their four nibbles in the LOW 16 BITS, element i at bits 4i.
+// t1 * 256 + t0 puts the four nibble bytes into four different bytes (order 0, 2, 1, 3) on top of known constant
+// bits; after subtracting those, (a >> 12) + a drops elements 1 and 3 between elements 0 and 2.  Three integer
+// multiply-adds (FMA pipe) for four elements.
+template <typename T>
+__device__ __forceinline__ uint32_t fold_quad(uint32_t t0, uint32_t t1) {
+  constexpr uint32_t kHalf = P2<T>::kHalfBits * 0x00010001u;
+  constexpr uint32_t kConst = kHalf + (kHalf << 8);
+  uint32_t v, a, u;
+  asm("mad.lo.u32 %0, %1, 256, %2;" : "=r"(v) : "r"(t1), "r"(t0));
+  asm("mad.lo.u32 %0, %1, 1, %2;" : "=r"(a) : "r"(v), "r"(0u - kConst));
+  asm("mad.hi.u32 %0, %1, %2, %1;" : "=r"(u) : "r"(a), "r"(1u << 20));  // (a >> 12) + a
+  return u;
+}
 // four folded pairs -> the packed word of 8 nibbles
 __device__ __forceinline__ uint32_t gather4(uint32_t u0, uint32_t u1, uint32_t u2, uint32_t u3) {
   return __byte_perm(__byte_perm(u0, u1, 0x0040), __byte_perm(u2, u3, 0x0040), 0x5410);
 }
 // 8 rounded z values held as 4 packed pairs -> packed word; CLAMP = false only when |z / s| < 7.5 is known
 template <typename T, bool CLAMP>
-__device__ __forceinline__ uint32_t quantize8(const uint32_t* zz, float s, float inv_s) {
-  uint32_t u[4];
+__device__ __forceinline__ uint32_t quantize8(const uint32_t* zz, float s, float inv_s, uint32_t hi2, uint32_t lo2) {
+  uint32_t t[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const uint32_t q = P2<T>::quot(P2<T>::lo(zz[i]), P2<T>::hi(zz[i]), s, inv_s);
-    u[i] = fold_pair<T>(CLAMP ? P2<T>::nibbles(q) : P2<T>::nibbles_inrange(q));
+    const uint32_t q = P2<T>::quotp(zz[i], s, inv_s, hi2, lo2);
+    t[i] = CLAMP ? P2<T>::nibbles(q) : P2<T>::nibbles_inrange(q);
   }
-  return gather4(u[0], u[1], u[2], u[3]);
+  return __byte_perm(fold_quad<T>(t[0], t[1]), fold_quad<T>(t[2], t[3]), 0x5410);
 }
 // round one float to the activation dtype through the packed convert (ALU pipe, short latency)
 template <typename T>

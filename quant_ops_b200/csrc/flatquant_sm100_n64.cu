@@ -285,6 +285,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       // round Z to the activation dtype once, as packed pairs; both passes work on the pairs
       uint32_t zz[16];
       float s = 1.f, inv_s = 1.f;
+      uint32_t rhi2 = 0, rlo2 = 0;  // 1/s as two packed terms of the activation dtype (bf16 only)
       bool clamp_needed = true;
       if (MODE != kTransform) {
 #pragma unroll
@@ -319,6 +320,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
         const float top = rnd1<T>(amax * clip);  // amax already is a value of the activation dtype
         s = fmaxf(rnd1<T>(top * 0.142857149f), DT<T>::floor_scale());
         inv_s = __frcp_rn(s);
+        P2<T>::recip2(inv_s, rhi2, rlo2);
         if (valid && mi == 0 && h == 0) store_scale(scales, tok, s, scale_dtype);
         // a quotient can only leave [-8, 7] after rounding if some |z| / s reaches 7.5; most warps have no such row
         clamp_needed = __any_sync(0xffffffffu, !(row_amax * inv_s < 7.4f));
@@ -340,10 +342,10 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
           uint32_t w[4];
           if (clamp_needed) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) w[j] = quantize8<T, true>(&zz[4 * j], s, inv_s);
+            for (int j = 0; j < 4; ++j) w[j] = quantize8<T, true>(&zz[4 * j], s, inv_s, rhi2, rlo2);
           } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) w[j] = quantize8<T, false>(&zz[4 * j], s, inv_s);
+            for (int j = 0; j < 4; ++j) w[j] = quantize8<T, false>(&zz[4 * j], s, inv_s, rhi2, rlo2);
           }
           if (valid) {
             uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(out) + tok * (feat / 8) + (mi * 64 + c0) / 8);
@@ -353,7 +355,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
           uint32_t pb[4], qb[4];
           if (!zero_scale) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) nibble_bytes_packed<T>(&zz[4 * j], s, inv_s, pb[j], qb[j]);
+            for (int j = 0; j < 4; ++j) nibble_bytes_packed<T>(&zz[4 * j], s, inv_s, rhi2, rlo2, pb[j], qb[j]);
           } else {
             // the reference divides by zero here: +-inf clamps to 7 / -8, 0/0 counts as 0
 #pragma unroll
