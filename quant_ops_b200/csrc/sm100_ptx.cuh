@@ -40,20 +40,31 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 // Bounded wait: gives up after `limit_polls` unsuccessful polls and returns false (the caller records the failure
-// and leaves); a healthy pipeline never gets near the limit.  The loop is three instructions.  No suspend-time
+// and leaves); a healthy pipeline never gets near the limit.  No suspend-time
 // hint is passed: with a hint a wait on an already completed phase was measured at 300-500 cycles instead of
 // under 100.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit_polls = 1u << 26) {
-  uint32_t ok = 0;
-  for (uint32_t polls = 0; polls < limit_polls; ++polls) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}\n"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    if (ok) return true;
-  }
-  return false;
+  // The whole loop is one PTX block with uniform branches (every polling lane reads the same barrier), two probes
+  // per trip: polling warps share issue slots with the warps that do the arithmetic, so the loop is kept short.
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .u32 n;\n\t"
+      "mov.u32 n, %3;\n"
+      "QO_WAIT_AGAIN:\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "@p bra.uni QO_WAIT_DONE;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "@p bra.uni QO_WAIT_DONE;\n\t"
+      "sub.u32 n, n, 2;\n\t"
+      "setp.gt.s32 p, n, 0;\n\t"
+      "@p bra.uni QO_WAIT_AGAIN;\n"
+      "QO_WAIT_DONE:\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(limit_polls) : "memory");
+  return ok != 0;
 }
 
 // Waits for two barriers at once.  A try_wait costs about 170 cycles even when the phase is already complete, so
@@ -61,18 +72,26 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
 // second barrier was the one still pending at the poll limit.
 __device__ __forceinline__ int mbar_wait2(uint32_t bar_a, uint32_t parity_a, uint32_t bar_b, uint32_t parity_b,
                                           uint32_t limit_polls = 1u << 26) {
-  uint32_t ok_a = 0, ok_b = 0;
-  for (uint32_t polls = 0; polls < limit_polls; ++polls) {
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%2], %3;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 q, [%4], %5;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "selp.u32 %1, 1, 0, q;\n\t}\n"
-        : "=r"(ok_a), "=r"(ok_b) : "r"(bar_a), "r"(parity_a), "r"(bar_b), "r"(parity_b) : "memory");
-    if (ok_a & ok_b) return 0;
-  }
-  return ok_a ? 2 : 1;
+  uint32_t ok_a, ok_b;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q, r;\n\t"
+      ".reg .u32 n;\n\t"
+      "mov.u32 n, %6;\n"
+      "QO_WAIT2_AGAIN:\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%2], %3;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 q, [%4], %5;\n\t"
+      "and.pred r, p, q;\n\t"
+      "@r bra.uni QO_WAIT2_DONE;\n\t"
+      "sub.u32 n, n, 1;\n\t"
+      "setp.gt.s32 r, n, 0;\n\t"
+      "@r bra.uni QO_WAIT2_AGAIN;\n"
+      "QO_WAIT2_DONE:\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "selp.u32 %1, 1, 0, q;\n\t"
+      "}\n"
+      : "=r"(ok_a), "=r"(ok_b) : "r"(bar_a), "r"(parity_a), "r"(bar_b), "r"(parity_b), "r"(limit_polls) : "memory");
+  return (ok_a & ok_b) ? 0 : (ok_a ? 2 : 1);
 }
 
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
