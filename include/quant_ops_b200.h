@@ -203,7 +203,8 @@ QO_API int qo_flatquant_quantize_host(const void* x_host, const void* left_host,
 QO_API uint64_t qo_kernel_launch_count(void);
 /* Which quantizer kernel the last qo_flatquant_quantize on this thread used: 0 none, 1 generic SIMT, 2 tcgen05. */
 QO_API int qo_last_quantizer_path(void);
-/* Which GEMM kernel the last qo_int4_matmul on this thread used: 0 none, 1 generic SIMT, 2 tcgen05. */
+/* Which GEMM kernel the last qo_int4_matmul on this thread used: 0 none, 1 generic SIMT, 2 tcgen05,
+ * 3 weight-streaming kernel for 1 .. 32 rows (automatic policy only). */
 QO_API int qo_last_gemm_path(void);
 /*
  * Kernel selection for the calling thread: 0 = automatic (tcgen05 kernel when the shape has one, else the

@@ -231,6 +231,11 @@ static int int4_matmul_impl(const int32_t* a, int64_t lda, const int32_t* b, int
   if (lda < k / 8) return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: lda smaller than k/8");
   int dev = 0, rc = require_device(&dev);
   if (rc) return rc;
+  // a few rows: stream the packed weights once instead of widening them for the tensor-memory kernel
+  if (t_policy == 0 && gemm_skinny_supported(t, k, n, a, lda, b, bsk, bsn)) {
+    t_gemm_path = 3;
+    return launch_gemm_skinny(a, lda, b, bsn, sa, sb, out, out_dtype, t, k, n, acc_out, bias, st);
+  }
   const bool fast_ok = k > 0 && gemm_sm100_supported(t, k, n, lda, bsk, bsn);
   if (t_policy == 2 && !fast_ok)
     return fail(QO_ERR_UNSUPPORTED, "int4_matmul: no tcgen05 kernel for t=%lld k=%lld n=%lld", (long long)t, (long long)k, (long long)n);

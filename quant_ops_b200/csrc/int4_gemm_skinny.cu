@@ -1,0 +1,239 @@
+// Packed-int4 GEMM for a handful of activation rows (decode steps: 1 .. 32 tokens), a weight-streaming kernel.
+//
+// With so few rows the product is bound by reading the packed weights once from HBM (Nout * K / 2 bytes); a
+// 128-row tcgen05 tile would spend at least three quarters of its rows on padding and would need the weights widened
+// to int8 in memory first, which doubles the bytes.  Here the weights stay packed all the way into registers:
+//
+//   * one CTA owns 16 or 32 output channels (rows of the [Nout, K/8] weight matrix); per 16 channels, 8 warps split
+//     K into 8 contiguous slices and add their partial sums through shared memory at the end;
+//   * a lane loads 16 bytes of a weight row at a time (four lanes cover 64 contiguous bytes of one row, a warp 16
+//     rows, consecutive loads of a warp walk along the rows), four chunks of 128 values per batch, and the next
+//     batch is requested before the current one is multiplied;
+//   * the activation rows (K / 2 bytes per token) are copied into shared memory once per CTA with cp.async while the
+//     first weight loads are in flight (rows padded by 64 bytes so that the fragment reads are conflict-free); with
+//     more tokens than fit, two row tiles share one copy (32 channels per CTA), and beyond that the rows are read
+//     through L1 / L2 instead;
+//   * nibbles become int8 operands without sign extension: x ^ 0x88888888 turns the offset-binary nibbles into
+//     two's-complement nibbles, and a nibble placed in the HIGH half of a byte is the int8 value 16 * n.  The even
+//     and the odd elements of a word make one operand register each; activations are treated identically, so both
+//     sides agree on the (permuted) order of K, and every product carries the factor 256, removed exactly by an
+//     arithmetic shift at the end (|256 * acc| < 2^31 for K <= 131072);
+//   * the products run on mma.sync m16n8k32 (int8): channels are the 16 rows, 8 tokens the columns.
+//
+// Arithmetic as in the reference kernel (src/quant_ops/ops/quantization/int4_matmul/kernels/
+// cuda_int4_matmul_kernel.cu:49-118): int32 accumulation, then (float(acc) * scale_a[row]) * scale_b[col].
+#include "qo_internal.cuh"
+
+namespace qo {
+namespace {
+
+constexpr int kSlices = 8;       // warps per 16 output channels: each takes a contiguous eighth of K
+constexpr int kChunkWords = 16;  // packed words of one weight row per chunk (4 lanes x 16 bytes)
+constexpr int kBatch = 4;        // chunks per batch of weight loads (two batches in flight)
+
+template <typename OutT>
+__device__ __forceinline__ OutT to_out(float v);
+template <>
+__device__ __forceinline__ __half to_out<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 to_out<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+__device__ __forceinline__ float from_out(__half v) { return __half2float(v); }
+__device__ __forceinline__ float from_out(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// packed word -> (even elements, odd elements) as int8 bytes holding 16 * value
+__device__ __forceinline__ void split16(uint32_t w, uint32_t& even, uint32_t& odd) {
+  const uint32_t t = w ^ 0x88888888u;
+  even = (t << 4) & 0xF0F0F0F0u;
+  odd = t & 0xF0F0F0F0u;
+}
+
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ld_stream(const uint32_t* p) {  // weights are read once: do not keep them in L1
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// NT = number of 8-token column tiles (tokens <= 8 * NT); RT = row tiles of 16 channels per CTA;
+// STAGED = activation rows are copied to shared memory (row stride nchunks * 64 + 64 bytes)
+template <int NT, int RT, bool STAGED, typename OutT>
+__global__ void __launch_bounds__(kSlices * RT * 32, RT == 1 ? 2 : 1)
+int4_gemm_skinny_kernel(const uint32_t* __restrict__ a, int64_t lda, const uint32_t* __restrict__ b, int64_t ldb,
+                        const float* __restrict__ sa, const float* __restrict__ sb, OutT* __restrict__ out,
+                        int32_t* __restrict__ acc_out, const OutT* __restrict__ bias, int tokens, int nchunks, int64_t n) {
+  constexpr int kThreads = kSlices * RT * 32;
+  __shared__ int red[kSlices * RT][NT][16][8 + 1];
+  extern __shared__ uint4 act[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+  const int rt = warp % RT, slice = warp / RT;
+  const int64_t n0 = ((int64_t)blockIdx.x * RT + rt) * 16;
+  const uint4 zero4 = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);  // eight zeros per word
+  const int stride4 = nchunks * 4 + 4;  // activation row stride in shared memory, in 16-byte units
+
+  if (STAGED) {
+    const int per_row = nchunks * 4, total = tokens * per_row;
+    const uint32_t base = (uint32_t)__cvta_generic_to_shared(act);
+    for (int p = threadIdx.x; p < total; p += kThreads) {
+      const int tok = p / per_row, q = p - tok * per_row;
+      cp_async16(base + (uint32_t)(tok * stride4 + q) * 16u, a + (int64_t)tok * lda + (int64_t)q * 4);
+    }
+  }
+
+  const int per = (nchunks + kSlices - 1) / kSlices;
+  const int cb = slice * per, ce = min(nchunks, cb + per);
+  const bool row0_ok = n0 + g < n, row1_ok = n0 + g + 8 < n;
+  const uint32_t* w0p = b + (n0 + g) * ldb + 4 * t4;
+  const uint32_t* w1p = b + (n0 + g + 8) * ldb + 4 * t4;
+  bool tok_ok[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) tok_ok[nt] = nt * 8 + g < tokens;
+
+  int acc[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[nt][i] = 0;
+
+  uint4 w0[2][kBatch], w1[2][kBatch];
+  auto load = [&](int buf, int c0) {
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int c = c0 + u;
+      w0[buf][u] = (c < ce && row0_ok) ? ld_stream(w0p + (int64_t)c * kChunkWords) : zero4;
+      w1[buf][u] = (c < ce && row1_ok) ? ld_stream(w1p + (int64_t)c * kChunkWords) : zero4;
+    }
+  };
+  auto compute = [&](int buf, int c0) {
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int c = c0 + u;
+      if (c >= ce) break;
+      uint4 x[NT];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        if (!tok_ok[nt]) x[nt] = zero4;
+        else if (STAGED) x[nt] = act[(nt * 8 + g) * stride4 + c * 4 + t4];
+        else x[nt] = __ldg(reinterpret_cast<const uint4*>(a + (int64_t)(nt * 8 + g) * lda + (int64_t)c * kChunkWords + 4 * t4));
+      }
+      const uint32_t w0w[4] = {w0[buf][u].x, w0[buf][u].y, w0[buf][u].z, w0[buf][u].w};
+      const uint32_t w1w[4] = {w1[buf][u].x, w1[buf][u].y, w1[buf][u].z, w1[buf][u].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t a0, a1, a2, a3;
+        split16(w0w[j], a0, a2);  // row g:     slots t4 (even elements) and 4 + t4 (odd elements)
+        split16(w1w[j], a1, a3);  // row g + 8
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const uint32_t xw = j == 0 ? x[nt].x : (j == 1 ? x[nt].y : (j == 2 ? x[nt].z : x[nt].w));
+          uint32_t b0, b1;
+          split16(xw, b0, b1);
+          mma_s8(acc[nt], a0, a1, a2, a3, b0, b1);
+        }
+      }
+    }
+  };
+
+  load(0, cb);
+  if (STAGED) {
+    cp_async_wait_all();
+    __syncthreads();
+  }
+  for (int c0 = cb; c0 < ce; c0 += 2 * kBatch) {
+    load(1, c0 + kBatch);
+    compute(0, c0);
+    load(0, c0 + 2 * kBatch);
+    compute(1, c0 + kBatch);
+  }
+
+  // fragment: c0 (row g, col 2 t4), c1 (row g, col 2 t4 + 1), c2 / c3 the same for row g + 8
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    red[warp][nt][g][2 * t4] = acc[nt][0];
+    red[warp][nt][g][2 * t4 + 1] = acc[nt][1];
+    red[warp][nt][g + 8][2 * t4] = acc[nt][2];
+    red[warp][nt][g + 8][2 * t4 + 1] = acc[nt][3];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < RT * NT * 128; idx += kThreads) {
+    const int r = idx & 15, col = (idx >> 4) & 7, nt = (idx >> 7) % NT, tile = idx / (NT * 128);
+    const int tok = nt * 8 + col;
+    const int64_t ch = ((int64_t)blockIdx.x * RT + tile) * 16 + r;
+    if (tok >= tokens || ch >= n) continue;
+    int sum = 0;
+#pragma unroll
+    for (int w = 0; w < kSlices; ++w) sum += red[w * RT + tile][nt][r][col];
+    sum >>= 8;  // both operands carried the factor 16
+    OutT v = to_out<OutT>(((float)sum * sa[tok]) * sb[ch]);
+    if (bias != nullptr) v = to_out<OutT>(from_out(v) + from_out(bias[ch]));
+    out[(int64_t)tok * n + ch] = v;
+    if (acc_out != nullptr) acc_out[(int64_t)tok * n + ch] = sum;
+  }
+}
+
+template <int NT, int RT, bool STAGED, typename OutT>
+int launch_cfg(const uint32_t* a, int64_t lda, const uint32_t* b, int64_t ldb, const float* sa, const float* sb, void* out,
+               int32_t* acc_out, const void* bias, int tokens, int nchunks, int64_t n, size_t smem, cudaStream_t stream) {
+  auto kern = int4_gemm_skinny_kernel<NT, RT, STAGED, OutT>;
+  if (smem > 0) {
+    int dev = 0;
+    QO_CUDA_TRY(cudaGetDevice(&dev));
+    static size_t configured[64] = {};
+    if (configured[dev & 63] < smem) {
+      QO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+      configured[dev & 63] = 200 * 1024;
+    }
+  }
+  const unsigned grid = (unsigned)((n + 16 * RT - 1) / (16 * RT));
+  kern<<<grid, kSlices * RT * 32, smem, stream>>>(a, lda, b, ldb, sa, sb, reinterpret_cast<OutT*>(out), acc_out,
+                                                  reinterpret_cast<const OutT*>(bias), tokens, nchunks, n);
+  return check_launch("int4_gemm_skinny_kernel");
+}
+
+template <int NT, typename OutT>
+int launch_nt(const uint32_t* a, int64_t lda, const uint32_t* b, int64_t ldb, const float* sa, const float* sb, void* out,
+              int32_t* acc_out, const void* bias, int tokens, int nchunks, int64_t n, cudaStream_t stream) {
+  const size_t stage = (size_t)tokens * ((size_t)nchunks * 64 + 64);
+  if (stage <= 92 * 1024)  // two CTAs of 16 channels per SM
+    return launch_cfg<NT, 1, true, OutT>(a, lda, b, ldb, sa, sb, out, acc_out, bias, tokens, nchunks, n, stage, stream);
+  if (stage <= 200 * 1024)  // one CTA of 32 channels per SM shares the copy
+    return launch_cfg<NT, 2, true, OutT>(a, lda, b, ldb, sa, sb, out, acc_out, bias, tokens, nchunks, n, stage, stream);
+  return launch_cfg<NT, 1, false, OutT>(a, lda, b, ldb, sa, sb, out, acc_out, bias, tokens, nchunks, n, 0, stream);
+}
+
+template <typename OutT>
+int launch_t(const uint32_t* a, int64_t lda, const uint32_t* b, int64_t ldb, const float* sa, const float* sb, void* out,
+             int32_t* acc_out, const void* bias, int tokens, int nchunks, int64_t n, cudaStream_t stream) {
+  if (tokens <= 8) return launch_nt<1, OutT>(a, lda, b, ldb, sa, sb, out, acc_out, bias, tokens, nchunks, n, stream);
+  if (tokens <= 16) return launch_nt<2, OutT>(a, lda, b, ldb, sa, sb, out, acc_out, bias, tokens, nchunks, n, stream);
+  return launch_nt<4, OutT>(a, lda, b, ldb, sa, sb, out, acc_out, bias, tokens, nchunks, n, stream);
+}
+
+}  // namespace
+
+// few rows, weights contiguous along K, K a multiple of 128, rows of both operands 16-byte aligned
+bool gemm_skinny_supported(int64_t t, int64_t k, int64_t n, const void* a, int64_t lda, const void* b, int64_t bsk, int64_t bsn) {
+  return t >= 1 && t <= 32 && n >= 1 && k >= 128 && k <= 131072 && (k % 128) == 0 && bsk == 1 && (bsn % 4) == 0 && (lda % 4) == 0 &&
+         (reinterpret_cast<uintptr_t>(a) % 16) == 0 && (reinterpret_cast<uintptr_t>(b) % 16) == 0 && n <= (int64_t)16 * 0x7fffffff;
+}
+
+int launch_gemm_skinny(const int32_t* a, int64_t lda, const int32_t* b, int64_t bsn, const float* sa, const float* sb, void* out,
+                       int out_dtype, int64_t t, int64_t k, int64_t n, int32_t* acc_out, const void* bias, cudaStream_t stream) {
+  const uint32_t* ua = reinterpret_cast<const uint32_t*>(a);
+  const uint32_t* ub = reinterpret_cast<const uint32_t*>(b);
+  const int nchunks = (int)(k / 128);
+  if (out_dtype == QO_F16) return launch_t<__half>(ua, lda, ub, bsn, sa, sb, out, acc_out, bias, (int)t, nchunks, n, stream);
+  if (out_dtype == QO_BF16) return launch_t<__nv_bfloat16>(ua, lda, ub, bsn, sa, sb, out, acc_out, bias, (int)t, nchunks, n, stream);
+  return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: out_dtype must be QO_F16 or QO_BF16");
+}
+
+}  // namespace qo

@@ -62,6 +62,34 @@ def test_accumulators_bit_exact_and_outputs(t, k, n, layout):
             np.testing.assert_array_equal(t2f(out), ref, err_msg=f"{label} outputs")
 
 
+SKINNY = [(1, 128, 16), (1, 4096, 4096), (5, 14336, 100), (8, 4096, 48), (9, 11008, 256), (16, 14336, 4096), (17, 256, 33),
+          (32, 4096, 512)]
+
+
+@pytest.mark.parametrize("t,k,n", SKINNY)
+def test_weight_streaming_kernel_for_few_rows(t, k, n):
+    """Automatic policy sends 1..32 rows against K-contiguous weights to the weight-streaming kernel."""
+    a, w, ap, wp, sa, sb = rand_problem(t, k, n, 3 * t + k + 5 * n)
+    acc_ref = O.int4_accumulators(ap.numpy(), wp.numpy().T)
+    apd, bd, sad, sbd = ap.to(DEV), wp.to(DEV).t(), sa.to(DEV), sb.to(DEV)
+    for out_dtype in ("fp16", "bf16"):
+        ref = O.round_to((acc_ref.astype(np.float32) * sa.numpy()[:, None]) * sb.numpy()[None, :], out_dtype)
+        out, acc = abi_int4_matmul(apd, bd, sad, sbd, out_dtype, True, policy=0)
+        assert lib.qo_last_gemm_path() == 3
+        np.testing.assert_array_equal(acc.cpu().numpy(), acc_ref)
+        np.testing.assert_array_equal(t2f(out), ref)
+    # extreme codes: every product is (-8) * (-8)
+    zeros_a = torch.zeros((t, k // 8), dtype=torch.int32, device=DEV)
+    zeros_w = torch.zeros((n, k // 8), dtype=torch.int32, device=DEV)
+    out, acc = abi_int4_matmul(zeros_a, zeros_w.t(), sad, sbd, "fp16", True, policy=0)
+    assert int(acc.min()) == int(acc.max()) == 64 * k
+    # rows that are views with a larger stride
+    wide = torch.zeros((t, k // 8 + 4), dtype=torch.int32, device=DEV)
+    wide[:, : k // 8] = apd
+    out2, acc2 = abi_int4_matmul(wide[:, : k // 8], bd, sad, sbd, "fp16", True, policy=0)
+    np.testing.assert_array_equal(acc2.cpu().numpy(), acc_ref)
+
+
 def test_extreme_codes_do_not_overflow():
     t, k, n = 64, 14336, 64
     ap = torch.full((t, k // 8), 0, dtype=torch.int32)          # all nibbles 0 -> code -8
