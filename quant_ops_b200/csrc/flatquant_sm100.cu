@@ -1,6 +1,9 @@
 // FlatQuant quantizer for sm_100a: TMA in, both Kronecker products on tcgen05 tensor cores with the accumulators in
 // tensor memory, scale + int4 codes straight from tensor memory to global memory with 16-byte stores.
 //
+// This is the shape-general kernel: it takes the N = 64 shapes whose M is not one of 16 / 32 / 48 / 64 (those run in
+// flatquant_sm100_n64.cu; N = 128 runs in flatquant_sm100_n128.cu) and holds the host-side dispatch for all three.
+//
 // One persistent CTA per SM.  A tile is G = floor(128 / M) whole tokens, i.e. G*M <= 128 rows of N elements.
 //
 //   warp 0      TMA producer: 3-D tensor map (n, m, token) -> X tile rows in shared memory, 128-byte swizzle
@@ -522,7 +525,8 @@ int launch_flatquant_sm100_mode(int mode, const void* x, int64_t ldx, const void
   const cuuint64_t dims[3] = {(cuuint64_t)n, (cuuint64_t)m, (cuuint64_t)tokens};
   const cuuint64_t strides[2] = {(cuuint64_t)n * 2, (cuuint64_t)ldx * 2};
   const bool batched = flatquant_sm100_n64_supported(m, n);  // groups of 2 tokens, stacked-L^T second product
-  const cuuint32_t box[3] = {64, (cuuint32_t)m, (cuuint32_t)(batched ? 2 : 128 / m)};
+  const bool wide = flatquant_sm100_n128_supported(m, n);     // right transform of size 128
+  const cuuint32_t box[3] = {64, (cuuint32_t)m, (cuuint32_t)(batched ? 2 : (wide ? flatquant_sm100_n128_group(m) : 128 / m))};
   const cuuint32_t estr[3] = {1, 1, 1};
   const CUresult r = encode_fn()(&map, in_dtype == QO_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
                                  3, const_cast<void*>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -532,12 +536,11 @@ int launch_flatquant_sm100_mode(int mode, const void* x, int64_t ldx, const void
 
   if (batched)
     return launch_flatquant_sm100_n64(mode, &map, left, right, codes, scales, tokens, m, clip, in_dtype, scale_dtype, status, stream);
-  if (in_dtype == QO_BF16) {
-    if (n == 64) return launch_mode<__nv_bfloat16, 64>(mode, map, left, right, codes, scales, tokens, m, clip, scale_dtype, status, stream);
-    return launch_mode<__nv_bfloat16, 128>(mode, map, left, right, codes, scales, tokens, m, clip, scale_dtype, status, stream);
-  }
-  if (n == 64) return launch_mode<__half, 64>(mode, map, left, right, codes, scales, tokens, m, clip, scale_dtype, status, stream);
-  return launch_mode<__half, 128>(mode, map, left, right, codes, scales, tokens, m, clip, scale_dtype, status, stream);
+  if (wide)
+    return launch_flatquant_sm100_n128(mode, &map, left, right, codes, scales, tokens, m, clip, in_dtype, scale_dtype, status, stream);
+  if (in_dtype == QO_BF16)
+    return launch_mode<__nv_bfloat16, 64>(mode, map, left, right, codes, scales, tokens, m, clip, scale_dtype, status, stream);
+  return launch_mode<__half, 64>(mode, map, left, right, codes, scales, tokens, m, clip, scale_dtype, status, stream);
 }
 
 int launch_flatquant_sm100(const void* x, int64_t ldx, const void* left, const void* right, void* codes, void* scales,

@@ -1,0 +1,432 @@
+// FlatQuant quantizer for sm_100a, right transform of size 128 (features = M x 128, 16 <= M <= 128): the hidden sizes
+// 14336 = 112 x 128, 11008 = 86 x 128 and 8192 = 64 x 128 run here.
+//
+// One persistent CTA per SM works on tiles of G tokens: G = 2 when M <= 64 and M is a multiple of 16, else G = 1.
+//
+//   warp 0       TMA: 3-D tensor map (n, m, token), two boxes of 64 x M x G per tile (the two 64-column halves of the
+//                rows), 128-byte swizzle, 2 stages
+//   warp 1       issues Y = X . R        A = X rows (K-major), B = R^T (K-major), M = 128, N = 128, K = 128
+//   warp 2       issues Z = LL . Y       A = LL (K-major): L^T in rows 0 .. M-1, and for G = 2 a second copy below it;
+//                                        B = Y (N-major).  G = 1: N = 128.  G = 2: one MMA of N = 256 per K step, the
+//                                        64-column blocks of both tokens interleaved along N, K = M
+//   warps 3-10   Y pass: tensor memory -> round to the activation dtype -> shared memory in the B layout;
+//                warp (q, h) handles columns 64h .. 64h+63 of tensor-memory lanes 32q .. 32q+31
+//   warps 11-26  quantize pass, 16 warps: warp (q, h) handles columns 32h .. 32h+31 of lanes 32q .. 32q+31; a thread
+//                rounds its 32 values once (packed pairs), the token's absmax is combined through shared memory, then
+//                scale, int4 codes and one 16-byte store.  The Z accumulators are released as soon as they sit in
+//                registers, so the next tile's second product overlaps with the arithmetic.
+//
+// With the stacked copy of L^T, lane block c holds the Z rows of token c, as in flatquant_sm100_n64.cu, whose packed
+// arithmetic (flatquant_sm100_common.cuh) this kernel shares.  Rows of a tile that only pad the reduction length of
+// the second product (M not a multiple of 16) are written as exact zeros by the Y pass.
+//
+// Rounding points and the exactness arguments are those of flatquant_sm100.cu (reference:
+// src/quant_ops/ops/quantization/flatquant/ops.py:99-117).  Every mbarrier wait is bounded.
+#include "flatquant_sm100_common.cuh"
+
+namespace qo {
+namespace {
+
+using namespace ptx;
+using namespace fq;
+
+constexpr int kThreads = 864;                  // 27 warps: TMA, two MMA issuers, 8 (Y pass) + 16 (quantize pass)
+constexpr int kEpi1Warp0 = 3, kEpi2Warp0 = 11;
+constexpr int kXStages = 2, kYStages = 2;      // kYStages also counts the Y accumulator stages
+constexpr int kStageBytes = 2 * kAtomBytes;    // 128 rows x 256 bytes, as two 64-column atoms
+constexpr int kOffX = 0;
+constexpr int kOffY = kOffX + kXStages * kStageBytes;
+constexpr int kOffR = kOffY + kYStages * kStageBytes;
+constexpr int kOffLL = kOffR + 2 * kAtomBytes;
+constexpr int kOffMisc = kOffLL + 2 * kAtomBytes;
+constexpr int kSmemBytes = kOffMisc + 1024 + 1024;
+constexpr int kTmemCols = 512;                 // Y accumulators: 2 stages x 128 columns; Z accumulators: 256 columns
+constexpr int kColZ = 256;
+
+struct Misc {
+  uint64_t full_x[kXStages], empty_x[kXStages];
+  uint64_t d1_full[kYStages], d1_empty[kYStages], y_full[kYStages], y_empty[kYStages];
+  uint64_t d2_full[2], d2_empty[2], set_sync;
+  uint32_t tmem_base;
+  int absmax_bits[3][2];
+};
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restrict__ left, const T* __restrict__ right,
+                      void* __restrict__ out, void* __restrict__ scales, long long tokens, int m, int group, float clip,
+                      int scale_dtype, uint32_t* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Misc* misc = reinterpret_cast<Misc*>(smem + kOffMisc);
+  const uint32_t smem_base = smem_u32(smem);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int rows_tile = group * m;            // X / Y rows per tile (<= 128)
+  const int k2 = (m + 15) & ~15;              // reduction length of the second product
+  const int y_atom = group == 2 ? 2 * m * 128 : kAtomBytes;  // bytes between the two 64-column halves of a Y stage
+  const long long ntiles = (tokens + group - 1) / group;
+  int mine = 0;                               // tiles this CTA works on
+  if ((long long)blockIdx.x < ntiles) mine = (int)((ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
+
+  if (tid == 0) {
+    for (int i = 0; i < kXStages; ++i) { mbar_init(smem_u32(&misc->full_x[i]), 1); mbar_init(smem_u32(&misc->empty_x[i]), 1); }
+    for (int i = 0; i < kYStages; ++i) {
+      mbar_init(smem_u32(&misc->d1_full[i]), 1);
+      mbar_init(smem_u32(&misc->d1_empty[i]), 8);   // one arrival per warp of the Y pass
+      mbar_init(smem_u32(&misc->y_full[i]), 8);
+      mbar_init(smem_u32(&misc->y_empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&misc->d2_full[i]), 1);
+      mbar_init(smem_u32(&misc->d2_empty[i]), 16);  // one arrival per warp of the quantize pass
+    }
+    mbar_init(smem_u32(&misc->set_sync), 16);
+    for (int i = 0; i < 3 * 2; ++i) (&misc->absmax_bits[0][0])[i] = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&x_map);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&misc->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();  // barriers and the tensor-memory base exist; the producer starts filling the X stages
+  tc_fence_after();
+  const uint32_t tmem = misc->tmem_base;
+
+  if (warp != 0) {
+    constexpr int kStagers = kThreads - 32;
+    const int t13 = tid - 32;
+    // raw copies of L and R into the (still unused) Y stages, all 16-byte loads in flight at once
+    uint16_t* raw_l = reinterpret_cast<uint16_t*>(smem + kOffY);
+    uint16_t* raw_r = reinterpret_cast<uint16_t*>(smem + kOffY + kStageBytes);
+    {
+      const int l_chunks = (m * m) / 8, r_chunks = 128 * 128 / 8;
+      constexpr int kMaxIter = (2 * 128 * 128 / 8 + kStagers - 1) / kStagers;
+      uint4 tmp[kMaxIter];
+#pragma unroll
+      for (int i = 0; i < kMaxIter; ++i) {
+        const int c = t13 + i * kStagers;
+        if (c < l_chunks) tmp[i] = reinterpret_cast<const uint4*>(left)[c];
+        else if (c - l_chunks < r_chunks) tmp[i] = reinterpret_cast<const uint4*>(right)[c - l_chunks];
+      }
+#pragma unroll
+      for (int i = 0; i < kMaxIter; ++i) {
+        const int c = t13 + i * kStagers;
+        if (c < l_chunks) reinterpret_cast<uint4*>(raw_l)[c] = tmp[i];
+        else if (c - l_chunks < r_chunks) reinterpret_cast<uint4*>(raw_r)[c - l_chunks] = tmp[i];
+      }
+      for (int i = l_chunks * 8 + t13; i < m * m; i += kStagers) raw_l[i] = reinterpret_cast<const uint16_t*>(left)[i];  // m * m not a multiple of 8
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kStagers) : "memory");
+    // R^T, K-major: row = output column n; its 16-byte chunk jc holds R[8jc .. 8jc+7][n].  Lanes walk n, so the
+    // 2-byte reads of a warp are contiguous and each thread makes one 16-byte swizzled store.
+    for (int idx = t13; idx < 128 * 16; idx += kStagers) {
+      const int n = idx & 127, jc = idx >> 7;
+      uint32_t w[4];
+#pragma unroll
+      for (int e2 = 0; e2 < 4; ++e2)
+        w[e2] = (uint32_t)raw_r[(8 * jc + 2 * e2) * 128 + n] | ((uint32_t)raw_r[(8 * jc + 2 * e2 + 1) * 128 + n] << 16);
+      *reinterpret_cast<uint4*>(smem + kOffR + (jc >> 3) * kAtomBytes + (n >> 3) * 1024 + (n & 7) * 128 + (((jc & 7) ^ (n & 7)) << 4)) =
+          make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    // LL, K-major: row (copy, i) = copy * mpad + i, column k holds L[k][i]; all other rows and the columns past m are zero
+    const int mpad = (m + 31) & ~31;  // the second copy starts on a 32-row boundary: a warp reads one token's columns
+    for (int idx = t13; idx < 128 * 16; idx += kStagers) {
+      const int r = idx & 127, kc = idx >> 7;
+      const int cpy = r / mpad, i = r - cpy * mpad;
+      const bool row_ok = cpy < group && i < m;
+      uint32_t w[4];
+#pragma unroll
+      for (int e2 = 0; e2 < 4; ++e2) {
+        const int k0 = 8 * kc + 2 * e2;
+        const uint32_t lo = (row_ok && k0 < m) ? raw_l[k0 * m + i] : 0u;
+        const uint32_t hi = (row_ok && k0 + 1 < m) ? raw_l[(k0 + 1) * m + i] : 0u;
+        w[e2] = lo | (hi << 16);
+      }
+      *reinterpret_cast<uint4*>(smem + kOffLL + (kc >> 3) * kAtomBytes + (r >> 3) * 1024 + (r & 7) * 128 + (((kc & 7) ^ (r & 7)) << 4)) =
+          make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    fence_proxy_async_smem();
+    asm volatile("bar.sync 1, %0;" ::"n"(kStagers) : "memory");
+  }
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint32_t bytes = (uint32_t)(rows_tile * 256);
+      int s = 0, ph = 0;
+      long long tile = blockIdx.x;
+      for (int it = 0; it < mine; ++it, tile += gridDim.x) {
+        if (!mbar_wait(smem_u32(&misc->empty_x[s]), ph ^ 1)) { atomicCAS(status, 0u, 0x900u + s); break; }
+        const uint32_t bar = smem_u32(&misc->full_x[s]);
+        mbar_arrive_expect_tx(bar, bytes);
+        tma_load_3d(smem_base + kOffX + s * kStageBytes, &x_map, bar, 0, 0, (int)(tile * group));
+        tma_load_3d(smem_base + kOffX + s * kStageBytes + kAtomBytes, &x_map, bar, 64, 0, (int)(tile * group));
+        if (++s == kXStages) { s = 0; ph ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc1 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 0, 0, 128, 128);
+      const uint64_t desc_x0 = umma_smem_desc_sw128(smem_base + kOffX, 16, 1024);
+      const uint64_t desc_r = umma_smem_desc_sw128(smem_base + kOffR, 16, 1024);
+      int sx = 0, phx = 0, s1 = 0, ph1 = 0;
+      for (int it = 0; it < mine; ++it) {
+        if (const int w = mbar_wait2(smem_u32(&misc->full_x[sx]), phx, smem_u32(&misc->d1_empty[s1]), ph1 ^ 1)) {
+          atomicCAS(status, 0u, 0x900u + 0x10u * w + sx);
+          break;
+        }
+        tc_fence_after();
+        const uint64_t da = desc_x0 + (uint64_t)(sx * (kStageBytes >> 4));
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t off = (uint64_t)((ks >> 2) * (kAtomBytes >> 4) + (ks & 3) * 2);  // K atom, then 32 bytes per step
+          mma_f16_ss(tmem + s1 * 128, da + off, desc_r + off, idesc1, ks);
+        }
+        mma_commit(smem_u32(&misc->empty_x[sx]));
+        mma_commit(smem_u32(&misc->d1_full[s1]));
+        if (++sx == kXStages) { sx = 0; phx ^= 1; }
+        if (++s1 == kYStages) { s1 = 0; ph1 ^= 1; }
+      }
+    }
+  } else if (warp == 2) {
+    if (lane == 0) {
+      const uint32_t idesc2 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 0, 1, 128, group == 2 ? 256 : 128);
+      const uint64_t desc_ll = umma_smem_desc_sw128(smem_base + kOffLL, 16, 1024);
+      // N-major B operand: the stride between 64-column blocks along N is m rows (G = 2: token blocks interleave
+      // with the column halves) or one atom (G = 1)
+      const uint64_t desc_y0 = umma_smem_desc_sw128(smem_base + kOffY, group == 2 ? (uint32_t)(m * 128) : (uint32_t)kAtomBytes, 1024);
+      const int ksteps2 = k2 >> 4;
+      int sy = 0, phy = 0;
+      for (int it = 0; it < mine; ++it) {
+        const int e = group == 2 ? 0 : (it & 1), ph = (group == 2 ? it : (it >> 1)) & 1;
+        if (const int w = mbar_wait2(smem_u32(&misc->y_full[sy]), phy, smem_u32(&misc->d2_empty[e]), ph ^ 1)) {
+          atomicCAS(status, 0u, 0x920u + 0x10u * w + sy);
+          break;
+        }
+        tc_fence_after();
+        const uint64_t db0 = desc_y0 + (uint64_t)(sy * (kStageBytes >> 4));
+#pragma unroll 1
+        for (int ks = 0; ks < ksteps2; ++ks) {
+          const uint64_t da2 = desc_ll + (uint64_t)((ks >> 2) * (kAtomBytes >> 4) + (ks & 3) * 2);
+          mma_f16_ss(tmem + kColZ + e * 128, da2, db0 + (uint64_t)(ks * 128), idesc2, ks);  // 16 Y rows = 2048 bytes per step
+        }
+        mma_commit(smem_u32(&misc->y_empty[sy]));
+        mma_commit(smem_u32(&misc->d2_full[e]));
+        if (++sy == kYStages) { sy = 0; phy ^= 1; }
+      }
+    }
+  } else if (warp < kEpi2Warp0) {
+    // ---- Y pass: 8 warps; warp (q, h) converts columns 64h .. 64h+63 of tensor-memory lanes 32q .. 32q+31 ------
+    const int q = warp & 3, h = (warp - kEpi1Warp0) >> 2, r = q * 32 + lane;
+    int s = 0, ph = 0;
+    for (int it = 0; it < mine; ++it) {
+      if (__any_sync(0xffffffffu, mbar_wait2(smem_u32(&misc->d1_full[s]), ph, smem_u32(&misc->y_empty[s]), ph ^ 1) != 0)) {
+        atomicCAS(status, 0u, 0xA00u + s);
+        break;
+      }
+      tc_fence_after();
+      uint8_t* yrow = smem + kOffY + s * kStageBytes + h * y_atom + r * 128;
+#pragma unroll
+      for (int p = 0; p < 2; ++p) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + s * 128 + h * 64 + p * 32, v);
+        tmem_ld_wait();
+        if (p == 1) {
+          tc_fence_before();
+          mbar_arrive_warp(smem_u32(&misc->d1_empty[s]));  // accumulators are in registers: the stage can be overwritten
+        }
+        if (r < rows_tile || (group == 1 && r < k2)) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 w = make_uint4(0, 0, 0, 0);  // rows that only pad the reduction length must be exact zeros
+            if (r < rows_tile) {
+              w.x = pack2<T>(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+              w.y = pack2<T>(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+              w.z = pack2<T>(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+              w.w = pack2<T>(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+            }
+            *reinterpret_cast<uint4*>(yrow + (((p * 4 + j) ^ (r & 7)) << 4)) = w;
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive_warp(smem_u32(&misc->y_full[s]));
+      if (++s == kYStages) { s = 0; ph ^= 1; }
+    }
+  } else {
+    // ---- quantize pass: 16 warps; warp (q, h) works on columns 32h .. 32h+31 of lanes 32q .. 32q+31 -----------
+    const int q = warp & 3, h = (warp - kEpi2Warp0) >> 2, l = q * 32 + lane;
+    const int mpad = (m + 31) & ~31;
+    const int c = l / mpad, mi = l - c * mpad;  // lane block c holds the Z rows of token c (copies start on warp boundaries)
+    const bool active = c < group && mi < m;
+    constexpr bool warp_uniform = true;         // all rows of a warp belong to one token
+    const int feat = m * 128;
+    const int c0 = h * 32;
+    // G = 1: two accumulator stages of 128 columns, natural column order.  G = 2: one stage of 256 columns whose
+    // 64-column blocks are ordered (half 0, token 0), (half 0, token 1), (half 1, token 0), (half 1, token 1).
+    const uint32_t col_in_stage = group == 2 ? (uint32_t)((((h >> 1) * 2 + (active ? c : 0)) * 64) + (h & 1) * 32) : (uint32_t)c0;
+    long long tile = blockIdx.x;
+    for (int it = 0; it < mine; ++it, tile += gridDim.x) {
+      const int e = group == 2 ? 0 : (it & 1), use = group == 2 ? it : (it >> 1);
+      const int buf = it % 3;
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&misc->d2_full[e]), use & 1))) { atomicCAS(status, 0u, 0xB00u + e); break; }
+      tc_fence_after();
+      const long long tok = tile * group + c;
+      const bool valid = active && tok < tokens;
+      uint32_t v[32];
+      tmem_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + kColZ + e * 128 + col_in_stage, v);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive_warp(smem_u32(&misc->d2_empty[e]));  // the Z accumulators of this stage are free again
+
+      if (MODE == kTransform) {
+        if (valid) {
+          float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + tok * feat + mi * 128 + c0);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            dst[j] = make_float4(DT<T>::rnd(__uint_as_float(v[4 * j])), DT<T>::rnd(__uint_as_float(v[4 * j + 1])),
+                                 DT<T>::rnd(__uint_as_float(v[4 * j + 2])), DT<T>::rnd(__uint_as_float(v[4 * j + 3])));
+        }
+        continue;
+      }
+
+      // round Z to the activation dtype once, as packed pairs; both passes work on the pairs
+      uint32_t zz[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) zz[i] = P2<T>::cvt(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+      uint32_t m0 = zz[0], m1 = zz[1], m2 = zz[2], m3 = zz[3];  // four chains keep the dependent latency short
+#pragma unroll
+      for (int i = 4; i < 16; i += 4) {
+        m0 = P2<T>::absmax(m0, zz[i]);
+        m1 = P2<T>::absmax(m1, zz[i + 1]);
+        m2 = P2<T>::absmax(m2, zz[i + 2]);
+        m3 = P2<T>::absmax(m3, zz[i + 3]);
+      }
+      m0 = P2<T>::absmax(P2<T>::absmax(m0, m1), P2<T>::absmax(m2, m3));
+      float amax = valid ? fmaxf(fabsf(P2<T>::lo(m0)), fabsf(P2<T>::hi(m0))) : 0.f;
+      const float row_amax = amax;  // this row's own extreme, used below to skip the clamp
+      if (warp_uniform) {
+        amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(amax)));  // non-negative floats order as integers
+        if (lane == 0 && active) atomicMax(&misc->absmax_bits[buf][c], __float_as_int(amax));
+      } else if (active) {
+        atomicMax(&misc->absmax_bits[buf][c], __float_as_int(amax));
+      }
+      // the 16 warps meet here (bounded); afterwards the slot holds the token's absmax
+      const uint32_t gs = smem_u32(&misc->set_sync);
+      mbar_arrive_warp(gs);
+      if (!__all_sync(0xffffffffu, mbar_wait(gs, it & 1))) { atomicCAS(status, 0u, 0xB10u); break; }
+      if (active) amax = __int_as_float(misc->absmax_bits[buf][c]);
+      if (h == 0 && l < 2) misc->absmax_bits[(it + 2) % 3][l] = 0;
+      // max of the rounded values = rounded max; clip * absmax and the division by 7 are rounded like the reference.
+      // top / 7 can neither hit nor come within 2^-13 (relative) of a midpoint of the 16-bit format, so the
+      // float32 product with 1/7 rounds to the same 16-bit value as the exact quotient.
+      const float top = rnd1<T>(amax * clip);  // amax already is a value of the activation dtype
+      const float s = fmaxf(rnd1<T>(top * 0.142857149f), DT<T>::floor_scale());
+      const float inv_s = __frcp_rn(s);
+      uint32_t rhi2, rlo2;  // 1/s as two packed terms of the activation dtype (bf16 only)
+      P2<T>::recip2(inv_s, rhi2, rlo2);
+      if (valid && mi == 0 && h == 0) store_scale(scales, tok, s, scale_dtype);
+      // a quotient can only leave [-8, 7] after rounding if some |z| / s reaches 7.5; most warps have no such row
+      const bool clamp_needed = __any_sync(0xffffffffu, !(row_amax * inv_s < 7.4f));
+      const bool zero_scale = s == 0.f;
+
+      if (MODE == kPacked && !zero_scale) {
+        uint32_t w[4];
+        if (clamp_needed) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) w[j] = quantize8<T, true>(&zz[4 * j], s, inv_s, rhi2, rlo2);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) w[j] = quantize8<T, false>(&zz[4 * j], s, inv_s, rhi2, rlo2);
+        }
+        if (valid) {
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(out) + tok * (feat / 8) + (mi * 128 + c0) / 8);
+          *dst = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      } else {
+        uint32_t pb[4], qb[4];
+        if (!zero_scale) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) nibble_bytes_packed<T>(&zz[4 * j], s, inv_s, rhi2, rlo2, pb[j], qb[j]);
+        } else {
+          // the reference divides by zero here: +-inf clamps to 7 / -8, 0/0 counts as 0
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            pb[j] = qb[j] = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t pz = zz[4 * j + (i >> 1)], qz = zz[4 * j + 2 + (i >> 1)];
+              const float z0 = (i & 1) ? P2<T>::hi(pz) : P2<T>::lo(pz), z1 = (i & 1) ? P2<T>::hi(qz) : P2<T>::lo(qz);
+              pb[j] |= (uint32_t)(z0 > 0.f ? 15 : (z0 < 0.f ? 0 : 8)) << (8 * i);
+              qb[j] |= (uint32_t)(z1 > 0.f ? 15 : (z1 < 0.f ? 0 : 8)) << (8 * i);
+            }
+          }
+        }
+        if (MODE == kPacked) {
+          if (valid) {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(out) + tok * (feat / 8) + (mi * 128 + c0) / 8);
+            *dst = make_uint4(pack8(pb[0], qb[0]), pack8(pb[1], qb[1]), pack8(pb[2], qb[2]), pack8(pb[3], qb[3]));
+          }
+        } else if (valid) {
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<int8_t*>(out) + tok * feat + mi * 128 + c0);
+          dst[0] = make_uint4(bytes4(pb[0]), bytes4(qb[0]), bytes4(pb[1]), bytes4(qb[1]));
+          dst[1] = make_uint4(bytes4(pb[2]), bytes4(qb[2]), bytes4(pb[3]), bytes4(qb[3]));
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+template <typename T, int MODE>
+int launch_one(const CUtensorMap& map, const void* left, const void* right, void* out, void* scales, int64_t tokens, int m,
+               float clip, int scale_dtype, uint32_t* status, cudaStream_t stream) {
+  auto kern = flatquant_n128_kernel<T, MODE>;
+  int dev = 0, sms = 148;
+  QO_CUDA_TRY(cudaGetDevice(&dev));
+  static bool configured[64] = {};
+  if (!configured[dev & 63]) {
+    QO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    configured[dev & 63] = true;
+  }
+  QO_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int group = flatquant_sm100_n128_group(m);
+  const int64_t ntiles = (tokens + group - 1) / group;
+  const int grid = (int)(ntiles < sms ? ntiles : sms);
+  kern<<<grid, kThreads, kSmemBytes, stream>>>(map, reinterpret_cast<const T*>(left), reinterpret_cast<const T*>(right), out,
+                                               scales, (long long)tokens, m, group, clip, scale_dtype, status);
+  return check_launch("flatquant_n128_kernel");
+}
+
+template <typename T>
+int launch_mode(int mode, const CUtensorMap& map, const void* left, const void* right, void* out, void* scales,
+                int64_t tokens, int m, float clip, int scale_dtype, uint32_t* status, cudaStream_t stream) {
+  switch (mode) {
+    case kInt8: return launch_one<T, kInt8>(map, left, right, out, scales, tokens, m, clip, scale_dtype, status, stream);
+    case kPacked: return launch_one<T, kPacked>(map, left, right, out, scales, tokens, m, clip, scale_dtype, status, stream);
+    default: return launch_one<T, kTransform>(map, left, right, out, scales, tokens, m, clip, scale_dtype, status, stream);
+  }
+}
+
+}  // namespace
+
+bool flatquant_sm100_n128_supported(int m, int n) { return n == 128 && m >= 16 && m <= 128; }
+int flatquant_sm100_n128_group(int m) { return (m <= 64 && (m % 16) == 0) ? 2 : 1; }
+
+int launch_flatquant_sm100_n128(int mode, const void* x_map, const void* left, const void* right, void* out, void* scales,
+                                int64_t tokens, int m, float clip, int in_dtype, int scale_dtype, uint32_t* status,
+                                cudaStream_t stream) {
+  const CUtensorMap& map = *reinterpret_cast<const CUtensorMap*>(x_map);
+  if (in_dtype == QO_BF16)
+    return launch_mode<__nv_bfloat16>(mode, map, left, right, out, scales, tokens, m, clip, scale_dtype, status, stream);
+  return launch_mode<__half>(mode, map, left, right, out, scales, tokens, m, clip, scale_dtype, status, stream);
+}
+
+}  // namespace qo

@@ -5,7 +5,7 @@
 //
 //   warp 0       TMA: 3-D tensor map (n, m, token), box 64 x M x 2 -> 2M rows of 128 bytes, 128-byte swizzle, 6 stages
 //   warp 1       issues Y = X . R        A = X rows (K-major), B = R^T (K-major), M = 128, N = 64, K = 64
-//   warp 2       issues Z = LL . Y2      A = LL = floor(128/M) copies of L^T stacked (K-major),
+//   warp 2       issues Z = LL . Y2      A = LL = 2 copies of L^T, each starting on a 32-row boundary (K-major),
 //                                        B = the 2 tokens' Y side by side along N (N-major, N = 128), K = M
 //   warps 3-10   Y pass: tensor memory -> round to the activation dtype -> shared memory in the B layout;
 //                warp (q, h) handles columns 32h..32h+31 of tensor-memory lanes 32q..32q+31
@@ -72,7 +72,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
   Misc* misc = reinterpret_cast<Misc*>(smem + kOffMisc);
   const uint32_t smem_base = smem_u32(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int copies = 128 / m;                 // copies of L^T stacked in the A operand of the second product (>= 2)
+  const int mpad = (m + 31) & ~31;            // each copy of L^T starts on a 32-lane boundary: a warp reads one token's columns
   const int rows_group = kGroup * m;          // X / Y rows per group (<= 128)
   const long long ngroups = (tokens + kGroup - 1) / kGroup;
   int mine = 0;                               // groups this CTA works on
@@ -138,18 +138,17 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
         w[e2] = (uint32_t)raw_r[(8 * jc + 2 * e2) * 64 + n] | ((uint32_t)raw_r[(8 * jc + 2 * e2 + 1) * 64 + n] << 16);
       *reinterpret_cast<uint4*>(smem + kOffR + (n >> 3) * 1024 + (n & 7) * 128 + ((jc ^ (n & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
     }
-    // LL, K-major: row (copy, i), column k holds L[k][i]; rows past the last copy and columns past m are zero
-    const int ll_rows = copies * m;
+    // LL, K-major: row (copy, i) = copy * mpad + i, column k holds L[k][i]; all other rows and the columns past m are zero
     for (int idx = t13; idx < 128 * 8; idx += kStagers) {
       const int r = idx & 127, kc = idx >> 7;
-      int i = r;
-      while (i >= m) i -= m;
+      const int cpy = r / mpad, i = r - cpy * mpad;
+      const bool row_ok = cpy < kGroup && i < m;
       uint32_t w[4];
 #pragma unroll
       for (int e2 = 0; e2 < 4; ++e2) {
         const int k0 = 8 * kc + 2 * e2;
-        const uint32_t lo = (r < ll_rows && k0 < m) ? raw_l[k0 * m + i] : 0u;
-        const uint32_t hi = (r < ll_rows && k0 + 1 < m) ? raw_l[(k0 + 1) * m + i] : 0u;
+        const uint32_t lo = (row_ok && k0 < m) ? raw_l[k0 * m + i] : 0u;
+        const uint32_t hi = (row_ok && k0 + 1 < m) ? raw_l[(k0 + 1) * m + i] : 0u;
         w[e2] = lo | (hi << 16);
       }
       *reinterpret_cast<uint4*>(smem + kOffLL + (r >> 3) * 1024 + (r & 7) * 128 + ((kc ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -262,9 +261,9 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
     // ---- quantize pass ---------------------------------------------------------------------------------------
     // set e (8 warps) takes the groups with (it & 1) == e; warp (q, h) of a set works on columns 32h .. 32h+31 of lanes 32q ..
     const int e = (warp - kEpi2Warp0) >> 3, q = warp & 3, h = ((warp - kEpi2Warp0) >> 2) & 1, l = q * 32 + lane;
-    const int c = l / m, mi = l - c * m;            // lane block c holds a copy of the Z rows: it serves token c
-    const bool active = c < kGroup;
-    const bool warp_uniform = (m & 31) == 0;
+    const int c = l / mpad, mi = l - c * mpad;      // lane block c holds a copy of the Z rows: it serves token c
+    const bool active = c < kGroup && mi < m;
+    constexpr bool warp_uniform = true;             // copies start on warp boundaries: all rows of a warp belong to one token
     const int feat = m * 64;
     long long grp = (long long)blockIdx.x + (long long)e * gridDim.x;
     for (int use = 0, it = e; it < mine; it += 2, ++use, grp += 2LL * gridDim.x) {

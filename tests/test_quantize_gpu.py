@@ -91,6 +91,29 @@ def test_against_oracle(tokens, feat, dtype, clip, pack, outliers):
         check(codes, scales, ref_codes, ref_scales, pack)
 
 
+WIDE = [(16, "bf16", 37, True), (32, "fp16", 9, False), (48, "bf16", 5, True), (64, "bf16", 131, True), (40, "bf16", 6, True),
+        (100, "fp16", 3, True), (112, "bf16", 300, True), (128, "bf16", 4, False), (86, "fp16", 150, False)]
+
+
+@pytest.mark.parametrize("m,dtype,tokens,pack", WIDE)
+def test_right_transform_of_size_128(m, dtype, tokens, pack):
+    """Explicit (M, 128) factorisations: tiles of two tokens (M <= 64, multiple of 16) and of one token, M not a
+    multiple of 16, odd and even token counts."""
+    x, left, right = make_inputs(tokens, m * 128, dtype, 31 * m + tokens, True, mn=(m, 128))
+    ref_codes, ref_scales = O.flatquant_quantize(t2f(x), t2f(left), t2f(right), 0.9, pack, dtype)
+    for label, codes, scales in run_both(x, left, right, 0.9, pack, dtype):
+        check(codes, scales, ref_codes, ref_scales, pack)
+
+
+@pytest.mark.parametrize("m,dtype,tokens,pack", [(16, "bf16", 41, True), (48, "bf16", 77, True), (48, "fp16", 6, False), (32, "bf16", 3, True)])
+def test_right_transform_of_size_64_small_left(m, dtype, tokens, pack):
+    """(M, 64) with M < 64, e.g. 3072 = 48 x 64: groups of two tokens whose rows do not fill whole warps."""
+    x, left, right = make_inputs(tokens, m * 64, dtype, 17 * m + tokens, True, mn=(m, 64))
+    ref_codes, ref_scales = O.flatquant_quantize(t2f(x), t2f(left), t2f(right), 0.9, pack, dtype)
+    for label, codes, scales in run_both(x, left, right, 0.9, pack, dtype):
+        check(codes, scales, ref_codes, ref_scales, pack)
+
+
 def test_activation_scale_config_sampled_rows():
     """8192 x 4096 bf16, 1 % outlier channels, clip 0.9, packed: every row quantized on the GPU, a seeded sample of
     rows compared with the oracle (rows are independent), and a dequantize round trip over everything."""
