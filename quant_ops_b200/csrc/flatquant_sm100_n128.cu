@@ -56,6 +56,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restrict__ left, const T* __restrict__ right,
                       void* __restrict__ out, void* __restrict__ scales, long long tokens, int m, int group, float clip,
                       int scale_dtype, uint32_t* __restrict__ status) {
+  grid_launch_dependents();  // a following launch of this kernel may set up its barriers and tensor memory early
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Misc* misc = reinterpret_cast<Misc*>(smem + kOffMisc);
@@ -93,6 +94,9 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
   __syncthreads();  // barriers and the tensor-memory base exist; the producer starts filling the X stages
   tc_fence_after();
   const uint32_t tmem = misc->tmem_base;
+  // Programmatic dependent launch: everything above overlaps with the tail of the preceding kernel of the stream;
+  // nothing below (reads of X, L, R, writes of the outputs) starts before that kernel has completed.
+  grid_dependency_wait();
 
   if (warp != 0) {
     constexpr int kStagers = kThreads - 32;
@@ -400,8 +404,18 @@ int launch_one(const CUtensorMap& map, const void* left, const void* right, void
   const int group = flatquant_sm100_n128_group(m);
   const int64_t ntiles = (tokens + group - 1) / group;
   const int grid = (int)(ntiles < sms ? ntiles : sms);
-  kern<<<grid, kThreads, kSmemBytes, stream>>>(map, reinterpret_cast<const T*>(left), reinterpret_cast<const T*>(right), out,
-                                               scales, (long long)tokens, m, group, clip, scale_dtype, status);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  QO_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, map, reinterpret_cast<const T*>(left), reinterpret_cast<const T*>(right), out, scales,
+                                 (long long)tokens, m, group, clip, scale_dtype, status));
   return check_launch("flatquant_n128_kernel");
 }
 

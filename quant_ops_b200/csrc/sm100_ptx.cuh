@@ -94,6 +94,12 @@ __device__ __forceinline__ int mbar_wait2(uint32_t bar_a, uint32_t parity_a, uin
   return (ok_a & ok_b) ? 0 : (ok_a ? 2 : 1);
 }
 
+// Programmatic dependent launch (a kernel launched with the programmatic-stream-serialization attribute may start
+// while its predecessor in the stream still runs): wait = block until the predecessor has completed and its
+// memory is visible (a no-op for an ordinary launch); launch_dependents = allow the successor to start early.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 // make generic-proxy writes to shared memory visible to the async proxy (TMA, tcgen05.mma operand reads)
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
