@@ -12,6 +12,11 @@ With N > 1 every rank runs the same workload on its own GPU (rows are independen
 
 `--impl reference` times the reference's CPU implementation of the same path (its torch CPU op chain, restated in
 oracle/torch_port.py) on the host cores, on a bounded sample of the workload.
+
+`--workload` selects one of the other measured cases of the path (single GPU, one JSON line each, same keys where
+they apply): `quantize_wide` (x [4096, 14336] bf16, 112 x 128 factors), `gemm` (packed int4 4096 x 4096 x 4096),
+`linear` (fused quantize + GEMM, 14336 -> 4096, `--tokens` rows; weights rotate over buffers larger than L2).
+The default, `quantize`, is the headline above.
 """
 from __future__ import annotations
 
@@ -273,6 +278,136 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def measured_tensor_peak():
+    """Dense int8 peak taken as twice the measured bf16 GEMM burst figure (int8 runs at twice the bf16 rate)."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            return 2.0 * float(json.load(fh)["bf16_tflops"]), "2 x measured bf16 burst (MEASURED_PEAKS.json)"
+    except Exception:
+        return 2.0 * 1590.0, "2 x fallback bf16 burst (earlier measurement on this pool)"
+
+
+def run_other(args):
+    """Secondary workloads: device-resident inputs, CUDA events around `steps` calls through the C ABI."""
+    import ctypes as C
+
+    import torch
+
+    from quant_ops_b200 import _native as nat
+
+    lib = nat.lib
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product path has no CPU fallback")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    stream = torch.cuda.current_stream()
+    sp = C.c_void_p(stream.cuda_stream)
+    vp = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None
+    g = torch.Generator(device="cpu").manual_seed(SEED)
+    hbm_peak, hbm_src = measured_peak()
+    tc_peak, tc_src = measured_tensor_peak()
+
+    if args.workload == "quantize_wide":
+        tokens, m, n = 4096, 112, 128
+        feat = m * n
+        x = torch.randn(tokens, feat, generator=g)
+        x[:, torch.randperm(feat, generator=g)[: feat // 100]] *= 50
+        left = torch.linalg.qr(torch.randn(m, m, dtype=torch.float64, generator=g)).Q.bfloat16().contiguous().to(dev)
+        right = torch.linalg.qr(torch.randn(n, n, dtype=torch.float64, generator=g)).Q.bfloat16().contiguous().to(dev)
+        nsets = 3  # 3 x 147 MB > L2
+        xs = [torch.roll(x, i, 0).bfloat16().to(dev) for i in range(nsets)]
+        codes = [torch.empty(tokens, feat // 8, dtype=torch.int32, device=dev) for _ in range(nsets)]
+        scales = [torch.empty(tokens, dtype=torch.float32, device=dev) for _ in range(nsets)]
+        algo = tokens * (feat * 2 + feat // 2 + 4) + (m * m + n * n) * 2
+
+        def step(i):
+            s = i % nsets
+            nat.check(lib.qo_flatquant_quantize(vp(xs[s]), feat, vp(left), vp(right), vp(codes[s]), vp(scales[s]), tokens, m, n,
+                                                CLIP, nat.QO_BF16, 1, nat.QO_F32, sp))
+
+        desc = {"workload": "flatquant_quantize x[4096,14336] bf16, 1% outlier channels x50, L 112x112 / R 128x128 orthogonal, clip 0.9, pack_int32",
+                "l2": "inputs rotate over 3 buffer sets (441 MB) > L2"}
+        metric, unit, scale_value = "flatquant_quantize_GBps", "GB/s", lambda sec: algo / sec / 1e9
+        roof = lambda v: {"bound": "hbm", "achieved": v, "peak": hbm_peak, "unit": "GB/s", "frac": v / hbm_peak, "traffic": None,
+                          "peak_source": hbm_src, "algorithmic_bytes_per_launch": algo}
+        dtype = "bf16"
+    else:
+        if args.workload == "gemm":
+            t, k, n_out = 4096, 4096, 4096
+        else:
+            t, k, n_out = int(args.tokens), 14336, 4096
+        nw = max(2, int(200e6 // (n_out * k // 2)) + 1)  # weight buffers that together exceed L2
+        wps = [torch.randint(-2**31, 2**31 - 1, (n_out, k // 8), generator=g, dtype=torch.int32).to(dev) for _ in range(nw)]
+        sw = (torch.rand(n_out, generator=g) * 0.01 + 0.001).to(dev)
+        out = torch.empty(t, n_out, dtype=torch.bfloat16, device=dev)
+        ops = 2.0 * t * k * n_out
+        if args.workload == "gemm":
+            ap = torch.randint(-2**31, 2**31 - 1, (t, k // 8), generator=g, dtype=torch.int32).to(dev)
+            sa = (torch.rand(t, generator=g) * 0.1 + 0.01).to(dev)
+            need = lib.qo_int4_matmul_workspace_bytes(t, k, n_out)
+            ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+
+            def step(i):
+                nat.check(lib.qo_int4_matmul(vp(ap), k // 8, vp(wps[i % nw]), 1, k // 8, vp(sa), vp(sw), vp(out), nat.QO_BF16, t, k,
+                                             n_out, None, vp(ws), need, sp))
+
+            desc = {"workload": "int4_matmul 4096 x 4096 x 4096 packed int4, bf16 out; the call widens both operands to int8, then runs the tcgen05 GEMM",
+                    "l2": f"weights rotate over {nw} buffers"}
+        else:
+            m, n = 112, 128
+            x = torch.randn(t, k, generator=g).bfloat16().to(dev)
+            left = torch.linalg.qr(torch.randn(m, m, dtype=torch.float64, generator=g)).Q.bfloat16().contiguous().to(dev)
+            right = torch.linalg.qr(torch.randn(n, n, dtype=torch.float64, generator=g)).Q.bfloat16().contiguous().to(dev)
+            need = lib.qo_w4a4_linear_workspace_bytes(t, k, n_out)
+            ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+
+            def step(i):
+                nat.check(lib.qo_w4a4_linear(vp(x), k, vp(left), vp(right), vp(wps[i % nw]), vp(sw), None, vp(out), t, m, n, n_out,
+                                             CLIP, nat.QO_BF16, nat.QO_BF16, vp(ws), need, sp))
+
+            desc = {"workload": f"w4a4_linear (quantize + packed int4 GEMM) {t} tokens, 14336 -> 4096, bf16 in / out",
+                    "l2": f"weights rotate over {nw} buffers ({nw * n_out * k // 2 // 10**6} MB) > L2"}
+        metric, unit, scale_value = "int4_matmul_TOPs", "TOP/s", lambda sec: ops / sec / 1e12
+        weight_bytes = n_out * k // 2
+
+        def roof(v):
+            r = {"bound": "tensor", "achieved": v, "peak": tc_peak, "unit": "TOP/s", "frac": v / tc_peak, "traffic": None,
+                 "peak_source": tc_src, "algorithmic_ops_per_launch": ops}
+            # few rows: the bound is reading the packed weights once
+            if t <= 256:
+                sec = ops / (v * 1e12)
+                gbs = weight_bytes / sec / 1e9
+                r = {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gbs / hbm_peak, "traffic": None,
+                     "peak_source": hbm_src, "algorithmic_bytes_per_launch": weight_bytes}
+            return r
+        dtype = "s4 x s4 -> s32"
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(physical_gpu_index(0))
+    sampler.start()
+    launches0 = lib.qo_kernel_launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for i in range(args.steps):
+        step(i)
+    ev1.record(stream)
+    torch.cuda.synchronize()
+    launches = lib.qo_kernel_launch_count() - launches0
+    clocks = sampler.stop()
+    sec = ev0.elapsed_time(ev1) / 1e3 / args.steps
+    if lib.qo_device_status(sp) != 0:
+        raise SystemExit("bench.py: device status " + str(lib.qo_last_error()))
+    value = scale_value(sec)
+    desc["gemm_kernel"] = {0: "-", 1: "generic SIMT", 2: "tcgen05", 3: "weight-streaming"}.get(lib.qo_last_gemm_path(), "?")
+    print(json.dumps({
+        "metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype,
+        "data": "synthetic", "config": desc, "roofline": roof(value), "gpu_launches": int(launches), "clocks": clocks,
+    }))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -280,6 +415,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="quantize", choices=["quantize", "quantize_wide", "gemm", "linear"])
+    ap.add_argument("--tokens", type=int, default=16, help="rows of the `linear` workload")
     args = ap.parse_args()
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
         # started by hand rather than by torchrun: start one rank per GPU ourselves
@@ -290,6 +427,8 @@ def main():
         raise SystemExit(subprocess.call(cmd))
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload != "quantize":
+        run_other(args)
     else:
         run_ours(args)
 

@@ -135,7 +135,7 @@ int launch_typed(const void* x, int64_t ldx, const void* left, const void* right
   if (smem > 200 * 1024) return fail(QO_ERR_UNSUPPORTED, "flatquant: m*n = %d is too large for the generic kernel", m * n);
   int dev = 0, sms = 148;
   QO_CUDA_TRY(cudaGetDevice(&dev));
-  QO_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  sms = sm_count(dev);
   const int per_sm = smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : 4);
   const int grid = (int)(tokens < (int64_t)sms * per_sm ? tokens : (int64_t)sms * per_sm);
   auto kern = pack == 2 ? flatquant_generic_kernel<T, 2> : (pack ? flatquant_generic_kernel<T, 1> : flatquant_generic_kernel<T, 0>);

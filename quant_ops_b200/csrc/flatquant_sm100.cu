@@ -472,7 +472,7 @@ int launch_one(const CUtensorMap& map, const void* left, const void* right, void
     QO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
     configured[dev & 63] = true;
   }
-  QO_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  sms = sm_count(dev);
   const int g = 128 / m;
   const int64_t ntiles = (tokens + g - 1) / g;
   const int grid = (int)(ntiles < sms ? ntiles : sms);

@@ -400,7 +400,7 @@ int launch_one(const CUtensorMap& map, const void* left, const void* right, void
     QO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     configured[dev & 63] = true;
   }
-  QO_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  sms = sm_count(dev);
   const int group = flatquant_sm100_n128_group(m);
   const int64_t ntiles = (tokens + group - 1) / group;
   const int grid = (int)(ntiles < sms ? ntiles : sms);

@@ -408,7 +408,7 @@ int launch_one(const CUtensorMap& map, const void* left, const void* right, void
     QO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     configured[dev & 63] = true;
   }
-  QO_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  sms = sm_count(dev);
   const int64_t ngroups = (tokens + kGroup - 1) / kGroup;
   const int grid = (int)(ngroups < sms ? ngroups : sms);
   cudaLaunchConfig_t cfg = {};

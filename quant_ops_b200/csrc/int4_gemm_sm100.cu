@@ -44,6 +44,28 @@ widen_rows_kernel(const uint32_t* __restrict__ in, int64_t ld_words, uint2* __re
   }
 }
 
+// The same for up to two operands in one launch, 16 bytes in and 32 bytes out per thread (rows 16-byte aligned,
+// K a multiple of 32): both operands of a GEMM are widened by one kernel.
+struct WidenJob {
+  const uint32_t* in;
+  uint4* out;
+  int64_t ld_words, rows, kquads;  // kquads = K / 32 = groups of four packed words per row
+};
+__global__ void __launch_bounds__(256)
+widen_rows2_kernel(WidenJob j0, WidenJob j1) {
+  const int64_t n0 = j0.rows * j0.kquads, total = n0 + j1.rows * j1.kquads;
+  for (int64_t i = blockIdx.x * 256LL + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
+    const bool second = i >= n0;
+    const WidenJob& j = second ? j1 : j0;
+    const int64_t e = second ? i - n0 : i;
+    const int64_t r = e / j.kquads, q = e - r * j.kquads;
+    const uint4 w = *reinterpret_cast<const uint4*>(j.in + r * j.ld_words + q * 4);
+    const uint2 a = widen8(w.x), b = widen8(w.y), c = widen8(w.z), d = widen8(w.w);
+    j.out[2 * e] = make_uint4(a.x, a.y, b.x, b.y);
+    j.out[2 * e + 1] = make_uint4(c.x, c.y, d.x, d.y);
+  }
+}
+
 // reference B layout [K/8, N] with N contiguous: transpose 32 x 32 words through shared memory so that both the
 // reads (along N) and the writes (along K) are contiguous
 __global__ void __launch_bounds__(256)
@@ -286,7 +308,7 @@ int launch_gemm_tile(const int8_t* a8, const int8_t* b8, const float* sa, const 
     QO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
     configured[dev & 63] = true;
   }
-  QO_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  sms = sm_count(dev);
   const int64_t ntiles = ((t + kBM - 1) / kBM) * ((n + BN - 1) / BN);
   const int grid = (int)(ntiles < sms ? ntiles : sms);
   kern<<<grid, kGemmThreads, C::kSmemBytes, stream>>>(a_map, b_map, sa, sb, reinterpret_cast<OutT*>(out), acc_out,
@@ -353,7 +375,20 @@ int launch_gemm_sm100(const int32_t* a, int64_t lda, const int32_t* b, int64_t b
     return fail(QO_ERR_WORKSPACE, "int4_matmul: workspace missing, too small or not 256-byte aligned");
   int8_t* a8 = reinterpret_cast<int8_t*>(workspace);
   int8_t* b8 = a8 + align256((size_t)t * k);
-  int rc = launch_widen_rows(a, lda, a8, t, k, stream);
+  int rc;
+  if (bsk == 1 && (k % 32) == 0 && (lda % 4) == 0 && (bsn % 4) == 0 && reinterpret_cast<uintptr_t>(a) % 16 == 0 &&
+      reinterpret_cast<uintptr_t>(b) % 16 == 0) {
+    // both operands have K contiguous and 16-byte aligned rows: one launch widens both
+    const WidenJob ja = {reinterpret_cast<const uint32_t*>(a), reinterpret_cast<uint4*>(a8), lda, t, k / 32};
+    const WidenJob jb = {reinterpret_cast<const uint32_t*>(b), reinterpret_cast<uint4*>(b8), bsn, n, k / 32};
+    const int64_t total = (t + n) * (k / 32);
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    widen_rows2_kernel<<<(int)blocks, 256, 0, stream>>>(ja, jb);
+    if ((rc = check_launch("widen_rows2_kernel"))) return rc;
+    return launch_gemm_sm100_s8(a8, b8, sa, sb, out, out_dtype, t, k, n, acc_out, bias, stream);
+  }
+  rc = launch_widen_rows(a, lda, a8, t, k, stream);
   if (rc) return rc;
   if (bsk == 1) {
     rc = launch_widen_rows(b, bsn, b8, n, k, stream);  // rows of the weight matrix [Nout, K/8]

@@ -38,6 +38,19 @@ inline int fail(int status, const char* fmt, ...) {
     }                                                                                       \
   } while (0)
 
+// number of SMs of a device, queried once per device (the attribute query costs about a microsecond per call)
+inline int sm_count(int dev) {
+  static std::atomic<int> cached[64];
+  int v = (dev >= 0 && dev < 64) ? cached[dev].load(std::memory_order_relaxed) : 0;
+  if (v > 0) return v;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) {
+    (void)cudaGetLastError();
+    return 148;
+  }
+  if (dev >= 0 && dev < 64) cached[dev].store(v, std::memory_order_relaxed);
+  return v;
+}
+
 inline int check_launch(const char* what) {
   cudaError_t e = cudaPeekAtLastError();
   if (e != cudaSuccess) {
