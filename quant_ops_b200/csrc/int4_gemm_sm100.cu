@@ -128,8 +128,8 @@ template <int BN, typename OutT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
                      const float* __restrict__ sa, const float* __restrict__ sb, OutT* __restrict__ out,
-                     int32_t* __restrict__ acc_out, const OutT* __restrict__ bias, int t, int n, int k,
-                     uint32_t* __restrict__ status) {
+                     int32_t* __restrict__ acc_out, const OutT* __restrict__ bias, int t, int n, int k, int ksplit,
+                     int32_t* __restrict__ part, uint32_t* __restrict__ status) {
   using C = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -137,7 +137,9 @@ gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_con
   const uint32_t smem_base = smem_u32(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tiles_n = (n + BN - 1) / BN, tiles_m = (t + kBM - 1) / kBM;
-  const int ntiles = tiles_m * tiles_n, ksteps = (k + kBK - 1) / kBK;
+  // A work item is an output tile and one of `ksplit` slices of K.  With ksplit > 1 the items add their int32
+  // partial sums into `part` (integer atomics: exact and order-independent) and a second kernel applies the scales.
+  const int ntiles = tiles_m * tiles_n * ksplit, ksteps = (k + kBK - 1) / kBK;
 
   if (tid == 0) {
     for (int i = 0; i < C::kStages; ++i) { mbar_init(smem_u32(&bars->full[i]), 1); mbar_init(smem_u32(&bars->empty[i]), 1); }
@@ -159,9 +161,11 @@ gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_con
     if (lane == 0) {
       int step = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < ntiles; tile += gridDim.x) {
+      for (int item = blockIdx.x; ok && item < ntiles; item += gridDim.x) {
+        const int tile = item / ksplit, kz = item - tile * ksplit;
         const int mb = tile / tiles_n, nb = tile - mb * tiles_n;
-        for (int ks = 0; ks < ksteps; ++ks, ++step) {
+        const int ks0 = (int)((long long)kz * ksteps / ksplit), ks1 = (int)((long long)(kz + 1) * ksteps / ksplit);
+        for (int ks = ks0; ks < ks1; ++ks, ++step) {
           const int s = step % C::kStages, ph = (step / C::kStages) & 1;
           if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1)) { atomicCAS(status, 0u, 0x500u + s); ok = false; break; }
           const uint32_t bar = smem_u32(&bars->full[s]);
@@ -177,11 +181,13 @@ gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_con
       const uint32_t idesc = umma_idesc(2, 1, 1, 0, 0, kBM, BN);  // s32 accumulators, s8 x s8, both K-major
       int step = 0, lt = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < ntiles; tile += gridDim.x, ++lt) {
+      for (int item = blockIdx.x; ok && item < ntiles; item += gridDim.x, ++lt) {
+        const int kz = item % ksplit;
+        const int ks0 = (int)((long long)kz * ksteps / ksplit), ks1 = (int)((long long)(kz + 1) * ksteps / ksplit);
         const int as = lt & 1, aph = (lt >> 1) & 1;
         if (!mbar_wait(smem_u32(&bars->acc_empty[as]), aph ^ 1)) { atomicCAS(status, 0u, 0x510u + as); break; }
         tc_fence_after();
-        for (int ks = 0; ks < ksteps; ++ks, ++step) {
+        for (int ks = ks0; ks < ks1; ++ks, ++step) {
           const int s = step % C::kStages, ph = (step / C::kStages) & 1;
           if (!mbar_wait(smem_u32(&bars->full[s]), ph)) { atomicCAS(status, 0u, 0x520u + s); ok = false; break; }
           tc_fence_after();
@@ -190,7 +196,7 @@ gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_con
           for (int j = 0; j < kBK / 32; ++j) {
             const uint64_t ad = umma_smem_desc_sw128(a_base + j * 32, 16, 1024);
             const uint64_t bd = umma_smem_desc_sw128(b_base + j * 32, 16, 1024);
-            mma_i8_ss(tmem + as * BN, ad, bd, idesc, (ks | j) != 0);
+            mma_i8_ss(tmem + as * BN, ad, bd, idesc, ((ks - ks0) | j) != 0);
           }
           mma_commit(smem_u32(&bars->empty[s]));
         }
@@ -201,7 +207,8 @@ gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_con
     const int q = warp & 3;
     float* sb_s = reinterpret_cast<float*>(smem + C::kOffSb) + (warp - 2) * BN;
     int lt = 0;
-    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++lt) {
+    for (int item = blockIdx.x; item < ntiles; item += gridDim.x, ++lt) {
+      const int tile = item / ksplit;
       const int mb = tile / tiles_n, nb = tile - mb * tiles_n;
       const int as = lt & 1, aph = (lt >> 1) & 1;
       const int row = mb * kBM + q * 32 + lane;
@@ -218,7 +225,14 @@ gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_con
         tmem_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + as * BN + c0, v);
         tmem_ld_wait();
         const int col0 = nb * BN + c0;
-        if (row_ok && col0 < n) {
+        if (part != nullptr) {
+          if (row_ok) {
+            int32_t* prow = part + (int64_t)row * n + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < n) atomicAdd(prow + j, (int)v[j]);
+          }
+        } else if (row_ok && col0 < n) {
           uint32_t w[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -261,6 +275,28 @@ gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_con
   }
 }
 
+// second step of a K-split GEMM: scales (and bias) applied to the summed int32 accumulators
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+gemm_finish_kernel(const int32_t* __restrict__ part, const float* __restrict__ sa, const float* __restrict__ sb,
+                   OutT* __restrict__ out, int32_t* __restrict__ acc_out, const OutT* __restrict__ bias, int64_t t, int64_t n) {
+  const int64_t total = t * n;
+  for (int64_t i = blockIdx.x * 256LL + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
+    const int64_t r = i / n, c = i - r * n;
+    const int acc = part[i];
+    const float f = ((float)acc * sa[r]) * sb[c];
+    uint32_t w = pack_out2<OutT>(f, 0.f);
+    if (bias != nullptr) {
+      const float2 o = unpack_out2(w, OutT());
+      uint32_t bw = 0;
+      *reinterpret_cast<OutT*>(&bw) = bias[c];
+      w = pack_out2<OutT>(o.x + unpack_out2(bw, OutT()).x, 0.f);
+    }
+    out[i] = *reinterpret_cast<OutT*>(&w);
+    if (acc_out != nullptr) acc_out[i] = acc;
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -294,7 +330,8 @@ int make_map_s8(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int
 
 template <int BN, typename OutT>
 int launch_gemm_tile(const int8_t* a8, const int8_t* b8, const float* sa, const float* sb, void* out, int32_t* acc_out,
-                     const void* bias, int64_t t, int64_t k, int64_t n, uint32_t* status, cudaStream_t stream) {
+                     const void* bias, int64_t t, int64_t k, int64_t n, uint32_t* status, cudaStream_t stream, int ksplit = 1,
+                     int32_t* part = nullptr) {
   using C = GemmCfg<BN>;
   CUtensorMap a_map, b_map;
   int rc = make_map_s8(&a_map, a8, t, k, kBM);
@@ -309,16 +346,42 @@ int launch_gemm_tile(const int8_t* a8, const int8_t* b8, const float* sa, const 
     configured[dev & 63] = true;
   }
   sms = sm_count(dev);
-  const int64_t ntiles = ((t + kBM - 1) / kBM) * ((n + BN - 1) / BN);
+  const int64_t ntiles = ((t + kBM - 1) / kBM) * ((n + BN - 1) / BN) * ksplit;
   const int grid = (int)(ntiles < sms ? ntiles : sms);
+  if (ksplit > 1) QO_CUDA_TRY(cudaMemsetAsync(part, 0, (size_t)t * n * sizeof(int32_t), stream));
   kern<<<grid, kGemmThreads, C::kSmemBytes, stream>>>(a_map, b_map, sa, sb, reinterpret_cast<OutT*>(out), acc_out,
-                                                     reinterpret_cast<const OutT*>(bias), (int)t, (int)n, (int)k, status);
-  return check_launch("gemm_s8_sm100_kernel");
+                                                     reinterpret_cast<const OutT*>(bias), (int)t, (int)n, (int)k, ksplit,
+                                                     ksplit > 1 ? part : nullptr, status);
+  if ((rc = check_launch("gemm_s8_sm100_kernel"))) return rc;
+  if (ksplit > 1) {
+    int64_t blocks = (t * n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    gemm_finish_kernel<OutT><<<(int)blocks, 256, 0, stream>>>(part, sa, sb, reinterpret_cast<OutT*>(out), acc_out,
+                                                             reinterpret_cast<const OutT*>(bias), t, n);
+    return check_launch("gemm_finish_kernel");
+  }
+  return QO_OK;
+}
+
+// K slices per output tile: few 128 x 256 tiles (a short activation matrix) leave most SMs idle and small tiles
+// re-read the activations once per column tile, so the tiles stay wide and K is split instead.
+int gemm_k_split(int64_t t, int64_t k, int64_t n) {
+  if (n < 256) return 1;
+  const int64_t tiles = ((t + kBM - 1) / kBM) * ((n + 255) / 256), ksteps = (k + kBK - 1) / kBK;
+  if (tiles >= 120) return 1;
+  int64_t split = 148 / tiles;
+  if (split > 8) split = 8;
+  if (split > ksteps / 8) split = ksteps / 8;
+  return split >= 2 ? (int)split : 1;
 }
 
 template <typename OutT>
 int launch_gemm_typed(const int8_t* a8, const int8_t* b8, const float* sa, const float* sb, void* out, int32_t* acc_out,
-                      const void* bias, int64_t t, int64_t k, int64_t n, uint32_t* status, cudaStream_t stream) {
+                      const void* bias, int64_t t, int64_t k, int64_t n, uint32_t* status, cudaStream_t stream,
+                      int32_t* part = nullptr) {
+  const int ksplit = part != nullptr ? gemm_k_split(t, k, n) : 1;
+  if (ksplit > 1)
+    return launch_gemm_tile<256, OutT>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, ksplit, part);
   // widest tile that does not leave most SMs idle
   const int64_t tiles_m = (t + kBM - 1) / kBM;
   if (n >= 256 && tiles_m * ((n + 255) / 256) >= 120)
@@ -334,7 +397,8 @@ inline size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 
 size_t gemm_sm100_workspace_bytes(int64_t t, int64_t k, int64_t n) {
   if (t <= 0 || k <= 0 || n <= 0) return 0;
-  return align256((size_t)t * k) + align256((size_t)n * k);
+  const size_t part = gemm_k_split(t, k, n) > 1 ? align256((size_t)t * n * sizeof(int32_t)) : 0;  // K-split partial sums
+  return align256((size_t)t * k) + align256((size_t)n * k) + part;
 }
 
 bool gemm_sm100_supported(int64_t t, int64_t k, int64_t n, int64_t lda, int64_t bsk, int64_t bsn) {
@@ -347,7 +411,7 @@ bool gemm_sm100_supported(int64_t t, int64_t k, int64_t n, int64_t lda, int64_t 
 }
 
 int launch_gemm_sm100_s8(const int8_t* a8, const int8_t* b8, const float* sa, const float* sb, void* out, int out_dtype,
-                         int64_t t, int64_t k, int64_t n, int32_t* acc_out, const void* bias, cudaStream_t stream) {
+                         int64_t t, int64_t k, int64_t n, int32_t* acc_out, const void* bias, cudaStream_t stream, int32_t* part) {
   if (reinterpret_cast<uintptr_t>(a8) % 16 || reinterpret_cast<uintptr_t>(b8) % 16 || reinterpret_cast<uintptr_t>(out) % 16 ||
       (acc_out && reinterpret_cast<uintptr_t>(acc_out) % 16) || (bias && reinterpret_cast<uintptr_t>(bias) % 4))
     return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: operands of the tcgen05 kernel must be 16-byte aligned");
@@ -355,8 +419,8 @@ int launch_gemm_sm100_s8(const int8_t* a8, const int8_t* b8, const float* sa, co
   QO_CUDA_TRY(cudaGetDevice(&dev));
   uint32_t* status = device_status_word(dev);
   if (!status) return fail(QO_ERR_CUDA, "int4_matmul: could not allocate the device status word");
-  if (out_dtype == QO_F16) return launch_gemm_typed<__half>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream);
-  return launch_gemm_typed<__nv_bfloat16>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream);
+  if (out_dtype == QO_F16) return launch_gemm_typed<__half>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, part);
+  return launch_gemm_typed<__nv_bfloat16>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, part);
 }
 
 int launch_widen_rows(const int32_t* in, int64_t ld_words, int8_t* out, int64_t rows, int64_t k, cudaStream_t stream) {
@@ -375,6 +439,7 @@ int launch_gemm_sm100(const int32_t* a, int64_t lda, const int32_t* b, int64_t b
     return fail(QO_ERR_WORKSPACE, "int4_matmul: workspace missing, too small or not 256-byte aligned");
   int8_t* a8 = reinterpret_cast<int8_t*>(workspace);
   int8_t* b8 = a8 + align256((size_t)t * k);
+  int32_t* part = gemm_k_split(t, k, n) > 1 ? reinterpret_cast<int32_t*>(b8 + align256((size_t)n * k)) : nullptr;
   int rc;
   if (bsk == 1 && (k % 32) == 0 && (lda % 4) == 0 && (bsn % 4) == 0 && reinterpret_cast<uintptr_t>(a) % 16 == 0 &&
       reinterpret_cast<uintptr_t>(b) % 16 == 0) {
@@ -386,7 +451,7 @@ int launch_gemm_sm100(const int32_t* a, int64_t lda, const int32_t* b, int64_t b
     if (blocks > 148 * 32) blocks = 148 * 32;
     widen_rows2_kernel<<<(int)blocks, 256, 0, stream>>>(ja, jb);
     if ((rc = check_launch("widen_rows2_kernel"))) return rc;
-    return launch_gemm_sm100_s8(a8, b8, sa, sb, out, out_dtype, t, k, n, acc_out, bias, stream);
+    return launch_gemm_sm100_s8(a8, b8, sa, sb, out, out_dtype, t, k, n, acc_out, bias, stream, part);
   }
   rc = launch_widen_rows(a, lda, a8, t, k, stream);
   if (rc) return rc;
@@ -399,7 +464,7 @@ int launch_gemm_sm100(const int32_t* a, int64_t lda, const int32_t* b, int64_t b
     rc = check_launch("widen_transpose_kernel");
   }
   if (rc) return rc;
-  return launch_gemm_sm100_s8(a8, b8, sa, sb, out, out_dtype, t, k, n, acc_out, bias, stream);
+  return launch_gemm_sm100_s8(a8, b8, sa, sb, out, out_dtype, t, k, n, acc_out, bias, stream, part);
 }
 
 // ---- pieces for callers that bring their own scratch and status word (int4_gemm_static.cu) ------------------------
