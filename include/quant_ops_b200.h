@@ -172,6 +172,27 @@ QO_API int qo_w4a4_linear(const void* x, int64_t ldx, const void* left, const vo
                           int out_dtype, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Layer form with weights prepared once.  The weights of a layer do not change between calls, so a host that can
+ * spend k bytes per output channel keeps them widened to int8 [n_out, k] (qo_prepare_weights, at load time) and the
+ * per-call work shrinks to: quantize the activations straight to int8 codes, then the tensor-core GEMM; no operand
+ * is rewritten per call.  Results are identical to qo_w4a4_linear.  Calls with at most 32 tokens read the packed
+ * weights instead (half the bytes), so both buffers are passed.
+ * Load-time counterpart in the reference: process_weights_after_loading, w4a4_flatquant_dynamic.py:268-304 (which
+ * packs; the int8 copy is this library's addition for sm_100a, where the tensor cores take int8).
+ *
+ *   prepared   qo_prepared_weights_bytes(n_out, k) bytes, 256-byte aligned, written by qo_prepare_weights
+ *   workspace  at least qo_w4a4_linear_prepared_workspace_bytes(); NULL = library-owned buffer
+ */
+QO_API size_t qo_prepared_weights_bytes(int64_t n_out, int64_t k);
+QO_API int qo_prepare_weights(const int32_t* w_packed, void* prepared, int64_t n_out, int64_t k, void* stream);
+QO_API size_t qo_w4a4_linear_prepared_workspace_bytes(int64_t tokens, int64_t k, int64_t n_out);
+QO_API int qo_w4a4_linear_prepared(const void* x, int64_t ldx, const void* left, const void* right,
+                                   const int32_t* w_packed, const void* prepared, const float* w_scale,
+                                   const void* bias, void* out, int64_t tokens, int m, int n, int64_t n_out,
+                                   float clip_ratio, int in_dtype, int out_dtype, void* workspace,
+                                   size_t workspace_bytes, void* stream);
+
+/*
  * int8 codes [rows, features] -> packed int32 [rows, features/8].
  * Stands in for: pack_int4_to_int32, src/quant_ops/ops/quantization/int4_matmul/ops.py:23-45.
  */

@@ -11,7 +11,8 @@ from __future__ import annotations
 from . import _native
 from .decompose import get_decompose_dim
 from .ops import (dequantize_int4, flatquant_cuda, flatquant_dynamic_quantize, int4_matmul, int4_matmul_cuda,
-                  int4_matmul_ex, pack_int4_to_int32, quantize_weights_int4, unpack_int32_to_int4, w4a4_linear)
+                  int4_matmul_ex, pack_int4_to_int32, prepare_weights, quantize_weights_int4, unpack_int32_to_int4, w4a4_linear,
+                  w4a4_linear_prepared)
 from . import meta as _meta  # noqa: F401  (registers the fake kernels)
 from . import sharding
 from .linear import W4A4Linear
@@ -29,6 +30,6 @@ CUDA_AVAILABLE = _cuda_available()
 
 __all__ = [
     "flatquant_dynamic_quantize", "flatquant_cuda", "dequantize_int4", "int4_matmul", "int4_matmul_cuda",
-    "int4_matmul_ex", "w4a4_linear", "get_decompose_dim", "pack_int4_to_int32", "unpack_int32_to_int4",
+    "int4_matmul_ex", "w4a4_linear", "w4a4_linear_prepared", "prepare_weights", "get_decompose_dim", "pack_int4_to_int32", "unpack_int32_to_int4",
     "quantize_weights_int4", "W4A4Linear", "sharding", "CUDA_AVAILABLE", "__version__",
 ]

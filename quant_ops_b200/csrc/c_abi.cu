@@ -299,6 +299,68 @@ int qo_w4a4_linear(const void* x, int64_t ldx, const void* left, const void* rig
                           reinterpret_cast<cudaStream_t>(stream));
 }
 
+size_t qo_prepared_weights_bytes(int64_t n_out, int64_t k) {
+  if (n_out <= 0 || k <= 0) return 0;
+  return align_up((size_t)n_out * (size_t)k, 256);
+}
+
+int qo_prepare_weights(const int32_t* w_packed, void* prepared, int64_t n_out, int64_t k, void* stream) {
+  clear_error();
+  if (n_out < 0 || k < 0 || k % 8) return fail(QO_ERR_INVALID_ARGUMENT, "prepare_weights: k (%lld) must be a non-negative multiple of 8", (long long)k);
+  if (n_out == 0 || k == 0) return QO_OK;
+  if (!w_packed || !prepared) return fail(QO_ERR_INVALID_ARGUMENT, "prepare_weights: null pointer argument");
+  if (reinterpret_cast<uintptr_t>(prepared) % 256) return fail(QO_ERR_INVALID_ARGUMENT, "prepare_weights: the prepared buffer must be 256-byte aligned");
+  int rc = require_device(nullptr);
+  if (rc) return rc;
+  return launch_widen_rows(w_packed, k / 8, reinterpret_cast<int8_t*>(prepared), n_out, k, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// layout of the prepared layer's workspace: int8 codes [tokens, k] | float scales [tokens] | K-split partial sums
+size_t qo_w4a4_linear_prepared_workspace_bytes(int64_t tokens, int64_t k, int64_t n_out) {
+  if (tokens <= 0 || k <= 0) return 0;
+  const size_t direct = align_up((size_t)tokens * (size_t)k, 256) + align_up((size_t)tokens * 4, 256) +
+                        (gemm_k_split(tokens, k, n_out) > 1 ? align_up((size_t)tokens * (size_t)n_out * 4, 256) : 0);
+  const size_t packed = qo_w4a4_linear_workspace_bytes(tokens, k, n_out);  // shapes that take the packed-weight route
+  return direct > packed ? direct : packed;
+}
+
+int qo_w4a4_linear_prepared(const void* x, int64_t ldx, const void* left, const void* right, const int32_t* w_packed,
+                            const void* prepared, const float* w_scale, const void* bias, void* out, int64_t tokens, int m,
+                            int n, int64_t n_out, float clip_ratio, int in_dtype, int out_dtype, void* workspace,
+                            size_t workspace_bytes, void* stream) {
+  clear_error();
+  if (n_out < 0) return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear: negative n_out");
+  const int64_t k = (int64_t)m * n;
+  if (m <= 0 || n <= 0 || k % 8) return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear: m*n must be a positive multiple of 8");
+  if (tokens == 0 || n_out == 0) return QO_OK;
+  if (!w_packed || !prepared || !w_scale || !out) return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear: null pointer argument");
+  if (out_dtype != QO_F16 && out_dtype != QO_BF16) return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear: out_dtype must be QO_F16 or QO_BF16");
+  int dev = 0, rc = require_device(&dev);
+  if (rc) return rc;
+  const size_t need = qo_w4a4_linear_prepared_workspace_bytes(tokens, k, n_out);
+  if (workspace == nullptr) {
+    if ((rc = scratch_get(g_scratch, dev, need, &workspace))) return rc;
+    workspace_bytes = need;
+  }
+  if (workspace_bytes < need) return fail(QO_ERR_WORKSPACE, "w4a4_linear: workspace of %zu bytes, need %zu", workspace_bytes, need);
+  // few tokens (weight-streaming kernel), or a shape / policy the int8 tensor-core kernel does not take: packed route
+  const bool direct = t_policy != 1 && tokens > 32 && gemm_sm100_supported(tokens, k, n_out, k / 8, 1, k / 8) &&
+                      reinterpret_cast<uintptr_t>(prepared) % 256 == 0;
+  if (!direct)
+    return qo_w4a4_linear(x, ldx, left, right, w_packed, w_scale, bias, out, tokens, m, n, n_out, clip_ratio, in_dtype, out_dtype,
+                          workspace, workspace_bytes, stream);
+  char* ws = reinterpret_cast<char*>(workspace);
+  int8_t* a8 = reinterpret_cast<int8_t*>(ws);
+  const size_t off_scale = align_up((size_t)tokens * (size_t)k, 256);
+  float* a_scale = reinterpret_cast<float*>(ws + off_scale);
+  int32_t* part = gemm_k_split(tokens, k, n_out) > 1 ? reinterpret_cast<int32_t*>(ws + off_scale + align_up((size_t)tokens * 4, 256)) : nullptr;
+  rc = qo_flatquant_quantize(x, ldx, left, right, a8, a_scale, tokens, m, n, clip_ratio, in_dtype, 0, QO_F32, stream);
+  if (rc) return rc;
+  t_gemm_path = 2;
+  return launch_gemm_sm100_s8(a8, reinterpret_cast<const int8_t*>(prepared), a_scale, w_scale, out, out_dtype, tokens, k, n_out,
+                              nullptr, bias, reinterpret_cast<cudaStream_t>(stream), part);
+}
+
 int qo_pack_int4(const int8_t* codes, int32_t* packed, int64_t rows, int64_t features, void* stream) {
   clear_error();
   if (rows < 0 || features < 0 || features % 8) return fail(QO_ERR_INVALID_ARGUMENT, "pack_int4: features (%lld) must be divisible by 8", (long long)features);

@@ -363,6 +363,8 @@ int launch_gemm_tile(const int8_t* a8, const int8_t* b8, const float* sa, const 
   return QO_OK;
 }
 
+}  // namespace
+
 // K slices per output tile: few 128 x 256 tiles (a short activation matrix) leave most SMs idle and small tiles
 // re-read the activations once per column tile, so the tiles stay wide and K is split instead.
 int gemm_k_split(int64_t t, int64_t k, int64_t n) {
@@ -374,6 +376,8 @@ int gemm_k_split(int64_t t, int64_t k, int64_t n) {
   if (split > ksteps / 8) split = ksteps / 8;
   return split >= 2 ? (int)split : 1;
 }
+
+namespace {
 
 template <typename OutT>
 int launch_gemm_typed(const int8_t* a8, const int8_t* b8, const float* sa, const float* sb, void* out, int32_t* acc_out,

@@ -163,6 +163,59 @@ at::Tensor w4a4_linear(const at::Tensor& x, const at::Tensor& left_trans, const 
   return out;
 }
 
+at::Tensor prepare_weights(const at::Tensor& w_packed) {
+  TORCH_CHECK(w_packed.is_cuda() && w_packed.dim() == 2 && w_packed.scalar_type() == at::kInt,
+              "prepare_weights: int32 CUDA [n_out, K/8] expected");
+  c10::cuda::CUDAGuard guard(w_packed.device());
+  at::Tensor w = w_packed.contiguous();
+  const int64_t n_out = w.size(0), k = w.size(1) * 8;
+  at::Tensor out = at::empty({n_out, k}, w.options().dtype(at::kChar));
+  check_status(qo_prepare_weights(w.data_ptr<int32_t>(), out.data_ptr(), n_out, k, current_stream()), "prepare_weights");
+  return out;
+}
+
+at::Tensor w4a4_linear_prepared(const at::Tensor& x, const at::Tensor& left_trans, const at::Tensor& right_trans,
+                                const at::Tensor& w_packed, const at::Tensor& w_prepared, const at::Tensor& w_scale,
+                                const c10::optional<at::Tensor>& bias, double clip_ratio,
+                                c10::optional<at::ScalarType> out_dtype_opt) {
+  TORCH_CHECK(x.is_cuda() && left_trans.is_cuda() && right_trans.is_cuda() && w_packed.is_cuda() && w_prepared.is_cuda() &&
+                  w_scale.is_cuda(), "w4a4_linear_prepared: all tensors must be CUDA tensors");
+  TORCH_CHECK(x.dim() == 2, "w4a4_linear_prepared: x must be [tokens, K]");
+  const int64_t m = left_trans.size(0), n = right_trans.size(0), k = m * n;
+  TORCH_CHECK(x.size(1) == k, "w4a4_linear_prepared: x last dimension must equal M*N");
+  TORCH_CHECK(left_trans.scalar_type() == x.scalar_type() && right_trans.scalar_type() == x.scalar_type(),
+              "w4a4_linear_prepared: transforms must have the dtype of x");
+  TORCH_CHECK(w_packed.dim() == 2 && w_packed.scalar_type() == at::kInt && w_packed.size(1) * 8 == k,
+              "w4a4_linear_prepared: w_packed must be int32 [n_out, K/8]");
+  TORCH_CHECK(w_prepared.dim() == 2 && w_prepared.scalar_type() == at::kChar && w_prepared.size(0) == w_packed.size(0) &&
+                  w_prepared.size(1) == k && w_prepared.is_contiguous(),
+              "w4a4_linear_prepared: w_prepared must be the contiguous int8 [n_out, K] tensor made by prepare_weights");
+  TORCH_CHECK(w_scale.scalar_type() == at::kFloat && w_scale.numel() == w_packed.size(0),
+              "w4a4_linear_prepared: w_scale must be float32 [n_out]");
+  const at::ScalarType out_dtype = out_dtype_opt.has_value() ? *out_dtype_opt : (x.scalar_type() == at::kBFloat16 ? at::kBFloat16 : at::kHalf);
+  TORCH_CHECK(out_dtype == at::kHalf || out_dtype == at::kBFloat16, "w4a4_linear_prepared: out_dtype must be float16 or bfloat16");
+  const int dt = to_qo_dtype(x.scalar_type(), "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor x2 = row_major(x), left = left_trans.contiguous(), right = right_trans.contiguous();
+  at::Tensor w = w_packed.contiguous(), ws_ = w_scale.reshape({-1}).contiguous();
+  at::Tensor b;
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->numel() == w.size(0), "w4a4_linear_prepared: bias must have n_out elements");
+    b = bias->to(out_dtype).contiguous();
+  }
+  const int64_t tokens = x2.size(0), n_out = w.size(0);
+  at::Tensor out = at::empty({tokens, n_out}, x.options().dtype(out_dtype));
+  const size_t ws_bytes = qo_w4a4_linear_prepared_workspace_bytes(tokens, k, n_out);
+  at::Tensor ws = at::empty({(int64_t)ws_bytes}, x.options().dtype(at::kByte));
+  check_status(qo_w4a4_linear_prepared(x2.data_ptr(), tokens > 1 ? x2.stride(0) : k, left.data_ptr(), right.data_ptr(),
+                                       w.data_ptr<int32_t>(), w_prepared.data_ptr(), ws_.data_ptr<float>(),
+                                       b.defined() ? b.data_ptr() : nullptr, out.data_ptr(), tokens, (int)m, (int)n, n_out,
+                                       (float)clip_ratio, dt, out_dtype == at::kHalf ? QO_F16 : QO_BF16,
+                                       ws_bytes ? ws.data_ptr() : nullptr, ws_bytes, current_stream()),
+               "w4a4_linear_prepared");
+  return out;
+}
+
 at::Tensor pack_int4(const at::Tensor& codes) {
   TORCH_CHECK(codes.is_cuda() && codes.scalar_type() == at::kChar && codes.dim() == 2, "pack_int4: int8 CUDA [rows, features] expected");
   TORCH_CHECK(codes.size(1) % 8 == 0, "features (", codes.size(1), ") must be divisible by 8");
@@ -203,6 +256,8 @@ TORCH_LIBRARY(quant_ops, m) {
   m.def("int4_matmul_ex(Tensor a, Tensor b, Tensor scale_a, Tensor scale_b, ScalarType out_dtype, bool return_acc=False) -> (Tensor, Tensor)");
   m.def("dequantize_int4(Tensor quantized, Tensor scales, bool packed_int32=False) -> Tensor");
   m.def("w4a4_linear(Tensor x, Tensor left_trans, Tensor right_trans, Tensor w_packed, Tensor w_scale, Tensor? bias=None, float clip_ratio=1, ScalarType? out_dtype=None) -> Tensor");
+  m.def("prepare_weights(Tensor w_packed) -> Tensor");
+  m.def("w4a4_linear_prepared(Tensor x, Tensor left_trans, Tensor right_trans, Tensor w_packed, Tensor w_prepared, Tensor w_scale, Tensor? bias=None, float clip_ratio=1, ScalarType? out_dtype=None) -> Tensor");
   m.def("pack_int4(Tensor codes) -> Tensor");
   m.def("unpack_int4(Tensor packed) -> Tensor");
   m.def("quantize_weights_int4(Tensor w) -> (Tensor, Tensor)");
@@ -214,6 +269,8 @@ TORCH_LIBRARY_IMPL(quant_ops, CUDA, m) {
   m.impl("int4_matmul_ex", &int4_matmul_ex);
   m.impl("dequantize_int4", &dequantize_int4);
   m.impl("w4a4_linear", &w4a4_linear);
+  m.impl("prepare_weights", &prepare_weights);
+  m.impl("w4a4_linear_prepared", &w4a4_linear_prepared);
   m.impl("pack_int4", &pack_int4);
   m.impl("unpack_int4", &unpack_int4);
   m.impl("quantize_weights_int4", &quantize_weights_int4);

@@ -18,8 +18,12 @@ from .decompose import get_decompose_dim
 
 class W4A4Linear(torch.nn.Module):
     def __init__(self, in_features: int, out_features: int, bias: bool = False, clip_ratio: float = 1.0,
-                 dtype: torch.dtype = torch.bfloat16, device=None):
+                 dtype: torch.dtype = torch.bfloat16, device=None, keep_int8_weights: bool = False):
+        """keep_int8_weights: also hold the weights widened to int8 [out, in] (twice the packed size); forward then
+        rewrites no operand per call.  The copy is made by load_quantized / load_float / prepare()."""
         super().__init__()
+        self.keep_int8_weights = bool(keep_int8_weights)
+        self.weight_int8 = None  # derived from weight_packed, not part of the state dict
         if in_features % 8:
             raise ValueError("in_features must be a multiple of 8 (eight int4 values per packed word)")
         self.in_features, self.out_features, self.clip_ratio = in_features, out_features, float(clip_ratio)
@@ -42,6 +46,12 @@ class W4A4Linear(torch.nn.Module):
         self.right_trans.copy_(right_trans)
         if bias is not None and self.bias is not None:
             self.bias.copy_(bias)
+        return self.prepare()
+
+    @torch.no_grad()
+    def prepare(self) -> "W4A4Linear":
+        """(Re)builds the int8 copy of the weights after weight_packed changed; a no-op without keep_int8_weights."""
+        self.weight_int8 = ops.prepare_weights(self.weight_packed) if self.keep_int8_weights else None
         return self
 
     @torch.no_grad()
@@ -55,7 +65,7 @@ class W4A4Linear(torch.nn.Module):
         self.right_trans.copy_(right_trans)
         if bias is not None and self.bias is not None:
             self.bias.copy_(bias)
-        return self
+        return self.prepare()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         lead = x.shape[:-1]
@@ -63,6 +73,10 @@ class W4A4Linear(torch.nn.Module):
         if x2.dtype != self.left_trans.dtype:
             raise RuntimeError(f"input dtype {x2.dtype} does not match the transforms' dtype {self.left_trans.dtype}")
         out_dtype = x2.dtype if x2.dtype in (torch.float16, torch.bfloat16) else torch.float16
-        y = ops.w4a4_linear(x2, self.left_trans, self.right_trans, self.weight_packed, self.weight_scale, self.bias,
-                            self.clip_ratio, out_dtype)
+        if self.weight_int8 is not None:
+            y = ops.w4a4_linear_prepared(x2, self.left_trans, self.right_trans, self.weight_packed, self.weight_int8,
+                                         self.weight_scale, self.bias, self.clip_ratio, out_dtype)
+        else:
+            y = ops.w4a4_linear(x2, self.left_trans, self.right_trans, self.weight_packed, self.weight_scale, self.bias,
+                                self.clip_ratio, out_dtype)
         return y.reshape(*lead, self.out_features)

@@ -48,6 +48,18 @@ def _linear_fake(x, left_trans, right_trans, w_packed, w_scale, bias=None, clip_
     return x.new_empty((x.size(0), w_packed.size(0)), dtype=out_dtype)
 
 
+@register_fake("quant_ops::prepare_weights")
+def _prepare_fake(w_packed):
+    return w_packed.new_empty((w_packed.size(0), w_packed.size(1) * 8), dtype=torch.int8)
+
+
+@register_fake("quant_ops::w4a4_linear_prepared")
+def _linear_prepared_fake(x, left_trans, right_trans, w_packed, w_prepared, w_scale, bias=None, clip_ratio=1.0, out_dtype=None):
+    if out_dtype is None:
+        out_dtype = torch.bfloat16 if x.dtype == torch.bfloat16 else torch.float16
+    return x.new_empty((x.size(0), w_packed.size(0)), dtype=out_dtype)
+
+
 @register_fake("quant_ops::pack_int4")
 def _pack_fake(codes):
     return codes.new_empty((codes.size(0), codes.size(1) // 8), dtype=torch.int32)

@@ -58,6 +58,19 @@ def w4a4_linear(x: torch.Tensor, left_trans: torch.Tensor, right_trans: torch.Te
     return _ops.w4a4_linear(x, left_trans, right_trans, w_packed, w_scale, bias, float(clip_ratio), out_dtype)
 
 
+def prepare_weights(w_packed: torch.Tensor) -> torch.Tensor:
+    """Packed weights [n_out, K/8] -> int8 [n_out, K], widened once at load time for w4a4_linear_prepared."""
+    return _ops.prepare_weights(w_packed)
+
+
+def w4a4_linear_prepared(x: torch.Tensor, left_trans: torch.Tensor, right_trans: torch.Tensor, w_packed: torch.Tensor,
+                         w_prepared: torch.Tensor, w_scale: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                         clip_ratio: float = 1.0, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """w4a4_linear with the weights also given as the int8 copy made by prepare_weights: same results, no per-call
+    rewriting of either operand (the activations are quantized straight to int8 codes)."""
+    return _ops.w4a4_linear_prepared(x, left_trans, right_trans, w_packed, w_prepared, w_scale, bias, float(clip_ratio), out_dtype)
+
+
 def pack_int4_to_int32(tensor: torch.Tensor) -> torch.Tensor:
     """int8 codes [rows, F] in [-8, 7] -> int32 [rows, F/8], nibble i of a word = code[8p+i] + 8."""
     return _ops.pack_int4(tensor)

@@ -1,10 +1,12 @@
 """The Python / torch-dispatcher layer on the GPU: same calls a user of the reference makes."""
+import ctypes as C
+
 import numpy as np
 import pytest
 import torch
 
 import quant_ops_b200 as q
-from helpers import compare_codes, compare_scales, make_inputs, t2f
+from helpers import N, compare_codes, compare_scales, make_inputs, t2f
 from oracle import w4a4_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -90,3 +92,23 @@ def test_w4a4_linear_module_matches_the_two_step_path():
     layer2 = q.W4A4Linear(4096, 256, bias=True, clip_ratio=0.9, dtype=torch.bfloat16, device=DEV)
     layer2.load_quantized(torch.from_numpy(wq), torch.from_numpy(sw), left.to(DEV), right.to(DEV), bias.to(DEV))
     assert torch.equal(layer2.weight_packed, layer.weight_packed) and torch.equal(layer2(x.to(DEV)), y.view(48, 256))
+
+
+@pytest.mark.parametrize("tokens,k,n_out", [(1, 4096, 256), (32, 4096, 512), (33, 4096, 256), (200, 14336, 512), (256, 4096, 4096),
+                                             (1100, 4096, 512)])
+def test_prepared_weights_give_identical_results(tokens, k, n_out):
+    """The layer with an int8 copy of its weights (no per-call widening of either operand) against the plain fused op:
+    few tokens (packed-weight route), K-split shapes and plain tiles."""
+    x, left, right = make_inputs(tokens, k, "bf16", 5 * tokens + n_out, True)
+    g = torch.Generator().manual_seed(tokens)
+    w = torch.randn(n_out, k, generator=g) * 0.02
+    bias = (torch.randn(n_out, generator=g) * 0.1).bfloat16().to(DEV)
+    plain = q.W4A4Linear(k, n_out, bias=True, clip_ratio=0.9, dtype=torch.bfloat16, device=DEV)
+    plain.load_float(w, left.to(DEV), right.to(DEV), bias)
+    kept = q.W4A4Linear(k, n_out, bias=True, clip_ratio=0.9, dtype=torch.bfloat16, device=DEV, keep_int8_weights=True)
+    kept.load_float(w, left.to(DEV), right.to(DEV), bias)
+    assert kept.weight_int8 is not None and kept.weight_int8.shape == (n_out, k)
+    assert torch.equal(kept.weight_int8, q.unpack_int32_to_int4(kept.weight_packed))
+    y0, y1 = plain(x.to(DEV)), kept(x.to(DEV))
+    assert torch.equal(y0, y1)
+    assert N.lib.qo_device_status(C.c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
