@@ -95,7 +95,8 @@ struct GemmCfg {
   static constexpr int kStageBytes = (kBM + BN) * kBK;
   static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int kOffSb = kStages * kStageBytes;           // 4 warps x BN floats
-  static constexpr int kOffBar = kOffSb + 4 * BN * 4;
+  static constexpr int kOffTr = kOffSb + 4 * BN * 4;             // 4 warps x 32 x 33 ints: transpose buffer of the K-split epilogue
+  static constexpr int kOffBar = kOffTr + 4 * 32 * 33 * 4;
   static constexpr int kSmemBytes = kOffBar + 256 + 1024;
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
 };
@@ -226,11 +227,18 @@ gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_con
         tmem_ld_wait();
         const int col0 = nb * BN + c0;
         if (part != nullptr) {
-          if (row_ok) {
-            int32_t* prow = part + (int64_t)row * n + col0;
+          // K-split: add this slice's partial sums.  A lane holds one row; going through shared memory turns the
+          // 32 x 32 block so that each atomic instruction of the warp covers 32 consecutive columns of one row.
+          int* tr = reinterpret_cast<int*>(smem + C::kOffTr) + (warp - 2) * (32 * 33);
+          __syncwarp();
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < n) atomicAdd(prow + j, (int)v[j]);
+          for (int j = 0; j < 32; ++j) tr[lane * 33 + j] = (int)v[j];
+          __syncwarp();
+          const int row0 = mb * kBM + q * 32;
+          if (col0 + lane < n) {
+#pragma unroll 4
+            for (int r = 0; r < 32; ++r)
+              if (row0 + r < t) atomicAdd(part + (int64_t)(row0 + r) * n + col0 + lane, tr[r * 33 + lane]);
           }
         } else if (row_ok && col0 < n) {
           uint32_t w[16];
@@ -275,25 +283,38 @@ gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_con
   }
 }
 
-// second step of a K-split GEMM: scales (and bias) applied to the summed int32 accumulators
+// second step of a K-split GEMM: scales (and bias) applied to the summed int32 accumulators, 8 outputs per thread
+// (n is a multiple of 8 on this path)
 template <typename OutT>
 __global__ void __launch_bounds__(256)
 gemm_finish_kernel(const int32_t* __restrict__ part, const float* __restrict__ sa, const float* __restrict__ sb,
                    OutT* __restrict__ out, int32_t* __restrict__ acc_out, const OutT* __restrict__ bias, int64_t t, int64_t n) {
-  const int64_t total = t * n;
+  const int64_t n8 = n / 8, total = t * n8;
   for (int64_t i = blockIdx.x * 256LL + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
-    const int64_t r = i / n, c = i - r * n;
-    const int acc = part[i];
-    const float f = ((float)acc * sa[r]) * sb[c];
-    uint32_t w = pack_out2<OutT>(f, 0.f);
+    const int64_t r = i / n8, c = (i - r * n8) * 8;
+    const int4 a0 = *reinterpret_cast<const int4*>(part + r * n + c), a1 = *reinterpret_cast<const int4*>(part + r * n + c + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(sb + c), s1 = *reinterpret_cast<const float4*>(sb + c + 4);
+    const float s_row = sa[r];
+    const int acc[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      w[j] = pack_out2<OutT>(((float)acc[2 * j] * s_row) * sc[2 * j], ((float)acc[2 * j + 1] * s_row) * sc[2 * j + 1]);
     if (bias != nullptr) {
-      const float2 o = unpack_out2(w, OutT());
-      uint32_t bw = 0;
-      *reinterpret_cast<OutT*>(&bw) = bias[c];
-      w = pack_out2<OutT>(o.x + unpack_out2(bw, OutT()).x, 0.f);
+      const uint4 bw = *reinterpret_cast<const uint4*>(bias + c);
+      const uint32_t b[4] = {bw.x, bw.y, bw.z, bw.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 o = unpack_out2(w[j], OutT()), bb = unpack_out2(b[j], OutT());
+        w[j] = pack_out2<OutT>(o.x + bb.x, o.y + bb.y);
+      }
     }
-    out[i] = *reinterpret_cast<OutT*>(&w);
-    if (acc_out != nullptr) acc_out[i] = acc;
+    *reinterpret_cast<uint4*>(out + r * n + c) = make_uint4(w[0], w[1], w[2], w[3]);
+    if (acc_out != nullptr) {
+      *reinterpret_cast<int4*>(acc_out + r * n + c) = a0;
+      *reinterpret_cast<int4*>(acc_out + r * n + c + 4) = a1;
+    }
   }
 }
 
@@ -354,7 +375,7 @@ int launch_gemm_tile(const int8_t* a8, const int8_t* b8, const float* sa, const 
                                                      ksplit > 1 ? part : nullptr, status);
   if ((rc = check_launch("gemm_s8_sm100_kernel"))) return rc;
   if (ksplit > 1) {
-    int64_t blocks = (t * n + 255) / 256;
+    int64_t blocks = (t * (n / 8) + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     gemm_finish_kernel<OutT><<<(int)blocks, 256, 0, stream>>>(part, sa, sb, reinterpret_cast<OutT*>(out), acc_out,
                                                              reinterpret_cast<const OutT*>(bias), t, n);
@@ -383,7 +404,9 @@ template <typename OutT>
 int launch_gemm_typed(const int8_t* a8, const int8_t* b8, const float* sa, const float* sb, void* out, int32_t* acc_out,
                       const void* bias, int64_t t, int64_t k, int64_t n, uint32_t* status, cudaStream_t stream,
                       int32_t* part = nullptr) {
-  const int ksplit = part != nullptr ? gemm_k_split(t, k, n) : 1;
+  // the finishing kernel of a K-split reads scale_b and bias 16 bytes at a time
+  const bool vec_ok = reinterpret_cast<uintptr_t>(sb) % 16 == 0 && (bias == nullptr || reinterpret_cast<uintptr_t>(bias) % 16 == 0);
+  const int ksplit = (part != nullptr && vec_ok) ? gemm_k_split(t, k, n) : 1;
   if (ksplit > 1)
     return launch_gemm_tile<256, OutT>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, ksplit, part);
   // widest tile that does not leave most SMs idle
