@@ -15,7 +15,9 @@ oracle/torch_port.py) on the host cores, on a bounded sample of the workload.
 
 `--workload` selects one of the other measured cases of the path (single GPU, one JSON line each, same keys where
 they apply): `quantize_wide` (x [4096, 14336] bf16, 112 x 128 factors), `gemm` (packed int4 4096 x 4096 x 4096),
-`linear` (fused quantize + GEMM, 14336 -> 4096, `--tokens` rows; weights rotate over buffers larger than L2).
+`linear` (fused quantize + GEMM, 14336 -> 4096, `--tokens` rows; weights rotate over buffers larger than L2),
+`stack` (the seven W4A4 projections of a Llama-3-8B layer over 65,536 tokens, rows split over the ranks, weights kept
+as int8 by `qo_prepare_weights`; tokens/s; the one secondary workload that also runs under torchrun).
 The default, `quantize`, is the headline above.
 """
 from __future__ import annotations
@@ -298,8 +300,17 @@ def run_other(args):
     lib = nat.lib
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the product path has no CPU fallback")
-    dev = torch.device("cuda", 0)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1 and args.workload != "stack":
+        raise SystemExit("bench.py: only the default workload and `stack` run on several GPUs")
+    dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
     stream = torch.cuda.current_stream()
     sp = C.c_void_p(stream.cuda_stream)
     vp = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None
@@ -307,7 +318,54 @@ def run_other(args):
     hbm_peak, hbm_src = measured_peak()
     tc_peak, tc_src = measured_tensor_peak()
 
-    if args.workload == "quantize_wide":
+    if args.workload == "stack":
+        total_tokens = 65536
+        tloc = total_tokens // world
+        chunk = min(tloc, 8192)
+        shapes = [("q", 4096, 4096), ("k", 4096, 1024), ("v", 4096, 1024), ("o", 4096, 4096), ("gate", 4096, 14336),
+                  ("up", 4096, 14336), ("down", 14336, 4096)]
+        g.manual_seed(SEED + rank)
+        gd = torch.Generator(device=dev).manual_seed(SEED + rank)  # activations are drawn on the device (1.2 G values)
+        xin = {k: torch.randn(tloc, k, generator=gd, device=dev, dtype=torch.bfloat16) for k in (4096, 14336)}
+        for k in xin:
+            xin[k][:, torch.randperm(k, generator=g)[: k // 100].to(dev)] *= 50
+        layers = []
+        ws_need = 0
+        for name, k, n_out in shapes:
+            m, n = (64, 64) if k == 4096 else (112, 128)
+            left = torch.linalg.qr(torch.randn(m, m, dtype=torch.float64, generator=g)).Q.bfloat16().contiguous().to(dev)
+            right = torch.linalg.qr(torch.randn(n, n, dtype=torch.float64, generator=g)).Q.bfloat16().contiguous().to(dev)
+            wp = torch.randint(-2**31, 2**31 - 1, (n_out, k // 8), generator=g, dtype=torch.int32).to(dev)
+            sw = (torch.rand(n_out, generator=g) * 0.01 + 0.001).to(dev)
+            w8 = torch.empty(lib.qo_prepared_weights_bytes(n_out, k), dtype=torch.uint8, device=dev)
+            nat.check(lib.qo_prepare_weights(vp(wp), vp(w8), n_out, k, sp))
+            out = torch.empty(tloc, n_out, dtype=torch.bfloat16, device=dev)
+            ws_need = max(ws_need, lib.qo_w4a4_linear_prepared_workspace_bytes(chunk, k, n_out))
+            layers.append((k, n_out, m, n, left, right, wp, w8, sw, out))
+        ws = torch.empty(ws_need, dtype=torch.uint8, device=dev)
+
+        def step(i):
+            for k, n_out, m, n, left, right, wp, w8, sw, out in layers:
+                x = xin[k]
+                for r0 in range(0, tloc, chunk):
+                    rows = min(chunk, tloc - r0)
+                    nat.check(lib.qo_w4a4_linear_prepared(C.c_void_p(x.data_ptr() + r0 * k * 2), k, vp(left), vp(right), vp(wp), vp(w8),
+                                                          vp(sw), None, C.c_void_p(out.data_ptr() + r0 * n_out * 2), rows, m, n, n_out,
+                                                          CLIP, nat.QO_BF16, nat.QO_BF16, vp(ws), ws_need, sp))
+
+        ops_per_token = 2.0 * sum(k * n_out for _, k, n_out in shapes)
+        desc = {"workload": "Llama-3-8B-shaped W4A4 projection stack (q, k, v, o, gate, up, down), 65,536 bf16 tokens split by rows over the ranks, "
+                            "per-layer random-orthogonal L/R, random int4 weights kept widened (qo_prepare_weights), outputs stay row-sharded",
+                "tokens_per_gpu": tloc, "parallelism": f"rows x{world}, no collective", "l2": "activations and outputs of a step are 8 GB per 65,536 tokens"}
+        metric, unit = "w4a4_stack_tokens_per_s", "tokens/s"
+        scale_value = lambda sec: total_tokens / sec
+        dtype = "bf16 -> s4 x s4 -> s32 -> bf16"
+
+        def roof(v):
+            tops = v / world * ops_per_token / 1e12
+            return {"bound": "tensor", "achieved": tops, "peak": tc_peak, "unit": "TOP/s", "frac": tops / tc_peak, "traffic": None,
+                    "peak_source": tc_src, "algorithmic_ops_per_token": ops_per_token}
+    elif args.workload == "quantize_wide":
         tokens, m, n = 4096, 112, 128
         feat = m * n
         x = torch.randn(tokens, feat, generator=g)
@@ -382,10 +440,15 @@ def run_other(args):
             return r
         dtype = "s4 x s4 -> s32"
 
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
     for i in range(max(3, args.warmup)):
         step(i)
-    torch.cuda.synchronize()
-    sampler = ClockSampler(physical_gpu_index(0))
+    barrier()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
     sampler.start()
     launches0 = lib.qo_kernel_launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -393,18 +456,25 @@ def run_other(args):
     for i in range(args.steps):
         step(i)
     ev1.record(stream)
-    torch.cuda.synchronize()
+    barrier()
     launches = lib.qo_kernel_launch_count() - launches0
     clocks = sampler.stop()
     sec = ev0.elapsed_time(ev1) / 1e3 / args.steps
     if lib.qo_device_status(sp) != 0:
         raise SystemExit("bench.py: device status " + str(lib.qo_last_error()))
+    if world > 1:
+        tmax = torch.tensor([sec], dtype=torch.float64, device=dev)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        sec = float(tmax[0])
+        dist.destroy_process_group()
+        if rank != 0:
+            return
     value = scale_value(sec)
     desc["gemm_kernel"] = {0: "-", 1: "generic SIMT", 2: "tcgen05", 3: "weight-streaming"}.get(lib.qo_last_gemm_path(), "?")
     print(json.dumps({
-        "metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
-        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype,
-        "data": "synthetic", "config": desc, "roofline": roof(value), "gpu_launches": int(launches), "clocks": clocks,
+        "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong" if args.workload == "stack" else "weak", "vs_baseline": None,
+        "dtype": dtype, "data": "synthetic", "config": desc, "roofline": roof(value), "gpu_launches": int(launches), "clocks": clocks,
     }))
 
 
@@ -415,7 +485,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="quantize", choices=["quantize", "quantize_wide", "gemm", "linear"])
+    ap.add_argument("--workload", default="quantize", choices=["quantize", "quantize_wide", "gemm", "linear", "stack"])
     ap.add_argument("--tokens", type=int, default=16, help="rows of the `linear` workload")
     args = ap.parse_args()
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
