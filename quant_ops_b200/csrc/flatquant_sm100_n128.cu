@@ -66,6 +66,15 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
   const int k2 = (m + 15) & ~15;              // reduction length of the second product
   const int y_atom = group == 2 ? 2 * m * 128 : kAtomBytes;  // bytes between the two 64-column halves of a Y stage
   const long long ntiles = (tokens + group - 1) / group;
+  // Warps whose 32 tensor-memory lanes carry no row of the tile take no part: they skip their role and the barrier
+  // counts below only include the others (M = 86: the fourth quadrant of both passes is idle).
+  const int mpad32 = (m + 31) & ~31;
+  const int nq1 = ((group == 1 ? k2 : rows_tile) + 31) >> 5;  // quadrants with rows in the Y pass
+  int nq2 = 0;                                                // quadrants with rows in the quantize pass
+  for (int qq = 0; qq < 4; ++qq) {
+    const int cc = (qq * 32) / mpad32;
+    nq2 += (cc < group && qq * 32 - cc * mpad32 < m) ? 1 : 0;
+  }
   int mine = 0;                               // tiles this CTA works on
   if ((long long)blockIdx.x < ntiles) mine = (int)((ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
 
@@ -73,15 +82,15 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
     for (int i = 0; i < kXStages; ++i) { mbar_init(smem_u32(&misc->full_x[i]), 1); mbar_init(smem_u32(&misc->empty_x[i]), 1); }
     for (int i = 0; i < kYStages; ++i) {
       mbar_init(smem_u32(&misc->d1_full[i]), 1);
-      mbar_init(smem_u32(&misc->d1_empty[i]), 8);   // one arrival per warp of the Y pass
-      mbar_init(smem_u32(&misc->y_full[i]), 8);
+      mbar_init(smem_u32(&misc->d1_empty[i]), 2 * nq1);  // one arrival per working warp of the Y pass
+      mbar_init(smem_u32(&misc->y_full[i]), 2 * nq1);
       mbar_init(smem_u32(&misc->y_empty[i]), 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&misc->d2_full[i]), 1);
-      mbar_init(smem_u32(&misc->d2_empty[i]), 16);  // one arrival per warp of the quantize pass
+      mbar_init(smem_u32(&misc->d2_empty[i]), 4 * nq2);  // one arrival per working warp of the quantize pass
     }
-    mbar_init(smem_u32(&misc->set_sync), 16);
+    mbar_init(smem_u32(&misc->set_sync), 4 * nq2);
     for (int i = 0; i < 3 * 2; ++i) (&misc->absmax_bits[0][0])[i] = 0;
     fence_barrier_init();
     prefetch_tensormap(&x_map);
@@ -224,7 +233,7 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
     // ---- Y pass: 8 warps; warp (q, h) converts columns 64h .. 64h+63 of tensor-memory lanes 32q .. 32q+31 ------
     const int q = warp & 3, h = (warp - kEpi1Warp0) >> 2, r = q * 32 + lane;
     int s = 0, ph = 0;
-    for (int it = 0; it < mine; ++it) {
+    for (int it = 0; it < (q < nq1 ? mine : 0); ++it) {
       if (__any_sync(0xffffffffu, mbar_wait2(smem_u32(&misc->d1_full[s]), ph, smem_u32(&misc->y_empty[s]), ph ^ 1) != 0)) {
         atomicCAS(status, 0u, 0xA00u + s);
         break;
@@ -271,7 +280,8 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
     // 64-column blocks are ordered (half 0, token 0), (half 0, token 1), (half 1, token 0), (half 1, token 1).
     const uint32_t col_in_stage = group == 2 ? (uint32_t)((((h >> 1) * 2 + (active ? c : 0)) * 64) + (h & 1) * 32) : (uint32_t)c0;
     long long tile = blockIdx.x;
-    for (int it = 0; it < mine; ++it, tile += gridDim.x) {
+    const bool warp_works = (q * 32) / mpad < group && q * 32 - ((q * 32) / mpad) * mpad < m;
+    for (int it = 0; it < (warp_works ? mine : 0); ++it, tile += gridDim.x) {
       const int e = group == 2 ? 0 : (it & 1), use = group == 2 ? it : (it >> 1);
       const int buf = it % 3;
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&misc->d2_full[e]), use & 1))) { atomicCAS(status, 0u, 0xB00u + e); break; }

@@ -76,6 +76,14 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
   const int mpad = (m + 31) & ~31;            // each copy of L^T starts on a 32-lane boundary: a warp reads one token's columns
   const int rows_group = kGroup * m;          // X / Y rows per group (<= 128)
   const long long ngroups = (tokens + kGroup - 1) / kGroup;
+  // Warps whose 32 tensor-memory lanes carry no row take no part: they skip their role and the barrier counts
+  // below only include the others (M = 32: the upper two quadrants of both passes are idle).
+  const int nq1 = (rows_group + 31) >> 5;     // quadrants with rows in the Y pass
+  int nq2 = 0;                                // quadrants with rows in the quantize pass
+  for (int qq = 0; qq < 4; ++qq) {
+    const int cc = (qq * 32) / mpad;
+    nq2 += (cc < kGroup && qq * 32 - cc * mpad < m) ? 1 : 0;
+  }
   int mine = 0;                               // groups this CTA works on
   if ((long long)blockIdx.x < ngroups) mine = (int)((ngroups - blockIdx.x + gridDim.x - 1) / gridDim.x);
 
@@ -83,14 +91,14 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
     for (int i = 0; i < kXStages; ++i) { mbar_init(smem_u32(&misc->full_x[i]), 1); mbar_init(smem_u32(&misc->empty_x[i]), 1); }
     for (int i = 0; i < kYStages; ++i) {
       mbar_init(smem_u32(&misc->d1_full[i]), 1);
-      mbar_init(smem_u32(&misc->d1_empty[i]), 8);  // one arrival per warp of the Y pass
-      mbar_init(smem_u32(&misc->y_full[i]), 8);
+      mbar_init(smem_u32(&misc->d1_empty[i]), 2 * nq1);  // one arrival per working warp of the Y pass
+      mbar_init(smem_u32(&misc->y_full[i]), 2 * nq1);
       mbar_init(smem_u32(&misc->y_empty[i]), 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&misc->d2_full[i]), 1);
-      mbar_init(smem_u32(&misc->d2_empty[i]), 8);  // one arrival per warp of a quantize set
-      mbar_init(smem_u32(&misc->set_sync[i]), 8);
+      mbar_init(smem_u32(&misc->d2_empty[i]), 2 * nq2);  // one arrival per working warp of a quantize set
+      mbar_init(smem_u32(&misc->set_sync[i]), 2 * nq2);
     }
     for (int i = 0; i < 2 * 3 * 8; ++i) (&misc->absmax_bits[0][0][0])[i] = 0;
     fence_barrier_init();
@@ -231,7 +239,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
     // ---- Y pass: 8 warps; warp (q, h) converts columns 32h .. 32h+31 of tensor-memory lanes 32q .. 32q+31 ------
     const int q = warp & 3, h = (warp - kEpi1Warp0) >> 2, r = q * 32 + lane;
     int s = 0, ph = 0;
-    for (int it = 0; it < mine; ++it) {
+    for (int it = 0; it < (q < nq1 ? mine : 0); ++it) {
       if (__any_sync(0xffffffffu, mbar_wait2(smem_u32(&misc->d1_full[s]), ph, smem_u32(&misc->y_empty[s]), ph ^ 1) != 0)) {
         atomicCAS(status, 0u, 0x700u + s);
         break;
@@ -270,7 +278,8 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
     constexpr bool warp_uniform = true;             // copies start on warp boundaries: all rows of a warp belong to one token
     const int feat = m * 64;
     long long grp = (long long)blockIdx.x + (long long)e * gridDim.x;
-    for (int use = 0, it = e; it < mine; it += 2, ++use, grp += 2LL * gridDim.x) {
+    const int mine_q = ((q * 32) / mpad < kGroup && q * 32 - ((q * 32) / mpad) * mpad < m) ? mine : 0;  // idle quadrants skip the pass
+    for (int use = 0, it = e; it < mine_q; it += 2, ++use, grp += 2LL * gridDim.x) {
       const int ph = use & 1, buf = use % 3;
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&misc->d2_full[e]), ph))) { atomicCAS(status, 0u, 0x800u + e); break; }
       tc_fence_after();
