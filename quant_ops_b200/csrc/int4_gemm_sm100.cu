@@ -283,6 +283,160 @@ gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_con
   }
 }
 
+// ---- 256 x 256 output tile per CTA: two 128-row accumulators share every B slice ------------------------------------
+// A 128 x 256 tile needs 48 KB of operands per 512 tensor-core cycles; taking two row blocks against the same 256
+// columns needs 64 KB per 1024 cycles, a third less per MMA, which is what the L2 -> shared-memory path can keep up
+// with.  The two accumulators fill tensor memory (2 x 256 columns), so the epilogue of a tile does not overlap the
+// next tile's main loop; sixteen epilogue warps (one per accumulator, lane quadrant and column half) keep it short.
+constexpr int kDualThreads = 576;  // TMA, MMA issuer, 16 epilogue warps
+struct DualCfg {
+  static constexpr int kStageBytes = (2 * kBM + 256) * kBK;  // A rows 0-127, A rows 128-255, B
+  static constexpr int kStages = 3;
+  static constexpr int kOffSb = kStages * kStageBytes;       // 16 warps x 128 floats
+  static constexpr int kOffBar = kOffSb + 16 * 128 * 4;
+  static constexpr int kSmemBytes = kOffBar + 256 + 1024;
+};
+
+template <typename OutT>
+__global__ void __launch_bounds__(kDualThreads, 1)
+gemm_s8_dual_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
+                    const float* __restrict__ sa, const float* __restrict__ sb, OutT* __restrict__ out,
+                    int32_t* __restrict__ acc_out, const OutT* __restrict__ bias, int t, int n, int k,
+                    uint32_t* __restrict__ status) {
+  using C = DualCfg;
+  constexpr int BN = 256, BM2 = 2 * kBM;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  GemmBars* bars = reinterpret_cast<GemmBars*>(smem + C::kOffBar);
+  const uint32_t smem_base = smem_u32(smem);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tiles_n = (n + BN - 1) / BN, tiles_m = (t + BM2 - 1) / BM2;
+  const int ntiles = tiles_m * tiles_n, ksteps = (k + kBK - 1) / kBK;
+
+  if (tid == 0) {
+    for (int i = 0; i < C::kStages; ++i) { mbar_init(smem_u32(&bars->full[i]), 1); mbar_init(smem_u32(&bars->empty[i]), 1); }
+    mbar_init(smem_u32(&bars->acc_full[0]), 1);
+    mbar_init(smem_u32(&bars->acc_empty[0]), 16);  // one arrival per epilogue warp
+    fence_barrier_init();
+    prefetch_tensormap(&a_map);
+    prefetch_tensormap(&b_map);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&bars->tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int step = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < ntiles; tile += gridDim.x) {
+        const int mb = tile / tiles_n, nb = tile - mb * tiles_n;
+        for (int ks = 0; ks < ksteps; ++ks, ++step) {
+          const int s = step % C::kStages, ph = (step / C::kStages) & 1;
+          if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1)) { atomicCAS(status, 0u, 0x540u + s); ok = false; break; }
+          const uint32_t bar = smem_u32(&bars->full[s]);
+          mbar_arrive_expect_tx(bar, C::kStageBytes);
+          const uint32_t dst = smem_base + s * C::kStageBytes;
+          tma_load_2d(dst, &a_map, bar, ks * kBK, mb * BM2);
+          tma_load_2d(dst + kBM * kBK, &a_map, bar, ks * kBK, mb * BM2 + kBM);
+          tma_load_2d(dst + 2 * kBM * kBK, &b_map, bar, ks * kBK, nb * BN);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(2, 1, 1, 0, 0, kBM, BN);  // s32 accumulators, s8 x s8, both K-major
+      int step = 0, lt = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < ntiles; tile += gridDim.x, ++lt) {
+        if (!mbar_wait(smem_u32(&bars->acc_empty[0]), (lt & 1) ^ 1)) { atomicCAS(status, 0u, 0x550u); break; }
+        tc_fence_after();
+        for (int ks = 0; ks < ksteps; ++ks, ++step) {
+          const int s = step % C::kStages, ph = (step / C::kStages) & 1;
+          if (!mbar_wait(smem_u32(&bars->full[s]), ph)) { atomicCAS(status, 0u, 0x560u + s); ok = false; break; }
+          tc_fence_after();
+          const uint32_t a0_base = smem_base + s * C::kStageBytes, a1_base = a0_base + kBM * kBK, b_base = a0_base + 2 * kBM * kBK;
+#pragma unroll
+          for (int j = 0; j < kBK / 32; ++j) {
+            const uint64_t bd = umma_smem_desc_sw128(b_base + j * 32, 16, 1024);
+            mma_i8_ss(tmem, umma_smem_desc_sw128(a0_base + j * 32, 16, 1024), bd, idesc, (ks | j) != 0);
+            mma_i8_ss(tmem + BN, umma_smem_desc_sw128(a1_base + j * 32, 16, 1024), bd, idesc, (ks | j) != 0);
+          }
+          mma_commit(smem_u32(&bars->empty[s]));
+        }
+        if (ok) mma_commit(smem_u32(&bars->acc_full[0]));
+      }
+    }
+  } else {
+    const int q = warp & 3, half = ((warp - 2) >> 2) & 1, ch = (warp - 2) >> 3;  // lane quadrant, accumulator (row block), column half
+    constexpr int kCols = BN / 2;
+    float* sb_s = reinterpret_cast<float*>(smem + C::kOffSb) + (warp - 2) * kCols;
+    int lt = 0;
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++lt) {
+      const int mb = tile / tiles_n, nb = tile - mb * tiles_n;
+      const int row = mb * BM2 + half * kBM + q * 32 + lane;
+      const bool row_ok = row < t;
+      const float s_row = row_ok ? sa[row] : 0.f;
+      __syncwarp();
+      for (int i = lane; i < kCols; i += 32) sb_s[i] = (nb * BN + ch * kCols + i < n) ? sb[nb * BN + ch * kCols + i] : 0.f;
+      __syncwarp();
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->acc_full[0]), lt & 1))) { atomicCAS(status, 0u, 0x570u); break; }
+      tc_fence_after();
+#pragma unroll 2
+      for (int cc = 0; cc < kCols; cc += 32) {
+        const int c0 = ch * kCols + cc;
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + half * BN + c0, v);
+        tmem_ld_wait();
+        const int col0 = nb * BN + c0;
+        if (row_ok && col0 < n) {
+          uint32_t w[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float f0 = ((float)(int)v[2 * j] * s_row) * sb_s[cc + 2 * j];
+            const float f1 = ((float)(int)v[2 * j + 1] * s_row) * sb_s[cc + 2 * j + 1];
+            w[j] = pack_out2<OutT>(f0, f1);
+          }
+          OutT* orow = out + (int64_t)row * n + col0;
+          if (bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (col0 + 2 * j < n) {
+                const float2 o = unpack_out2(w[j], OutT());
+                const float2 b = unpack_out2(*reinterpret_cast<const uint32_t*>(bias + col0 + 2 * j), OutT());
+                w[j] = pack_out2<OutT>(o.x + b.x, o.y + b.y);
+              }
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (col0 + 8 * j < n) reinterpret_cast<uint4*>(orow)[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+          if (acc_out != nullptr) {
+            int32_t* arow = acc_out + (int64_t)row * n + col0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (col0 + 4 * j < n) reinterpret_cast<uint4*>(arow)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive_warp(smem_u32(&bars->acc_empty[0]));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
 // second step of a K-split GEMM: scales (and bias) applied to the summed int32 accumulators, 8 outputs per thread
 // (n is a multiple of 8 on this path)
 template <typename OutT>
@@ -386,6 +540,29 @@ int launch_gemm_tile(const int8_t* a8, const int8_t* b8, const float* sa, const 
 
 }  // namespace
 
+template <typename OutT>
+int launch_gemm_dual(const int8_t* a8, const int8_t* b8, const float* sa, const float* sb, void* out, int32_t* acc_out,
+                     const void* bias, int64_t t, int64_t k, int64_t n, uint32_t* status, cudaStream_t stream) {
+  CUtensorMap a_map, b_map;
+  int rc = make_map_s8(&a_map, a8, t, k, kBM);
+  if (rc) return rc;
+  if ((rc = make_map_s8(&b_map, b8, n, k, 256))) return rc;
+  auto kern = gemm_s8_dual_kernel<OutT>;
+  int dev = 0;
+  QO_CUDA_TRY(cudaGetDevice(&dev));
+  static bool configured[64] = {};
+  if (!configured[dev & 63]) {
+    QO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DualCfg::kSmemBytes));
+    configured[dev & 63] = true;
+  }
+  const int sms = sm_count(dev);
+  const int64_t ntiles = ((t + 2 * kBM - 1) / (2 * kBM)) * ((n + 255) / 256);
+  const int grid = (int)(ntiles < sms ? ntiles : sms);
+  kern<<<grid, kDualThreads, DualCfg::kSmemBytes, stream>>>(a_map, b_map, sa, sb, reinterpret_cast<OutT*>(out), acc_out,
+                                                            reinterpret_cast<const OutT*>(bias), (int)t, (int)n, (int)k, status);
+  return check_launch("gemm_s8_dual_kernel");
+}
+
 // K slices per output tile: few 128 x 256 tiles (a short activation matrix) leave most SMs idle and small tiles
 // re-read the activations once per column tile, so the tiles stay wide and K is split instead.
 int gemm_k_split(int64_t t, int64_t k, int64_t n) {
@@ -409,6 +586,12 @@ int launch_gemm_typed(const int8_t* a8, const int8_t* b8, const float* sa, const
   const int ksplit = (part != nullptr && vec_ok) ? gemm_k_split(t, k, n) : 1;
   if (ksplit > 1)
     return launch_gemm_tile<256, OutT>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, ksplit, part);
+  // enough 256 x 256 tiles for every SM: two accumulators per CTA share each B slice
+  // (with few tiles and a short K the unshared tile does better: its epilogue overlaps the next main loop and its
+  // smaller tiles fill the last wave more evenly)
+  const int64_t tiles2 = ((t + 2 * kBM - 1) / (2 * kBM)) * ((n + 255) / 256);
+  if (n >= 256 && tiles2 >= 140 && (k >= 8192 || tiles2 >= 4 * 148))
+    return launch_gemm_dual<OutT>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream);
   // widest tile that does not leave most SMs idle
   const int64_t tiles_m = (t + kBM - 1) / kBM;
   if (n >= 256 && tiles_m * ((n + 255) / 256) >= 120)
