@@ -46,7 +46,10 @@ def test_against_reference_fixtures(name):
 
 SHAPES = [(1, 64, 8), (1, 4096, 4096), (16, 14336, 512), (128, 256, 256), (129, 1000 * 8, 130), (300, 4096, 520),
           (1024, 1024, 1024), (256, 14336, 4096), (77, 8, 5),
-          (2200, 8192, 4104), (4096, 512, 9472)]  # the two-accumulator kernel: long K with ragged tiles, many tiles
+          # the two-accumulator kernel: long K with ragged tiles, many tiles
+          (2200, 8192, 4104), (4096, 512, 9472),
+          # 512 tiles of 128 x 256 on 148 SMs, exact and with a ragged last column tile
+          (4096, 256, 4096), (4096, 256, 3848)]
 
 
 @pytest.mark.parametrize("t,k,n", SHAPES)
