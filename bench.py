@@ -416,14 +416,24 @@ def run_other(args):
             x = torch.randn(t, k, generator=g).bfloat16().to(dev)
             left = torch.linalg.qr(torch.randn(m, m, dtype=torch.float64, generator=g)).Q.bfloat16().contiguous().to(dev)
             right = torch.linalg.qr(torch.randn(n, n, dtype=torch.float64, generator=g)).Q.bfloat16().contiguous().to(dev)
-            need = lib.qo_w4a4_linear_workspace_bytes(t, k, n_out)
+            if args.prepared:
+                need = lib.qo_w4a4_linear_prepared_workspace_bytes(t, k, n_out)
+                w8s = [torch.empty(lib.qo_prepared_weights_bytes(n_out, k), dtype=torch.uint8, device=dev) for _ in range(nw)]
+                for wp, w8 in zip(wps, w8s):
+                    nat.check(lib.qo_prepare_weights(vp(wp), vp(w8), n_out, k, sp))
+            else:
+                need = lib.qo_w4a4_linear_workspace_bytes(t, k, n_out)
             ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
 
             def step(i):
-                nat.check(lib.qo_w4a4_linear(vp(x), k, vp(left), vp(right), vp(wps[i % nw]), vp(sw), None, vp(out), t, m, n, n_out,
-                                             CLIP, nat.QO_BF16, nat.QO_BF16, vp(ws), need, sp))
+                if args.prepared:
+                    nat.check(lib.qo_w4a4_linear_prepared(vp(x), k, vp(left), vp(right), vp(wps[i % nw]), vp(w8s[i % nw]), vp(sw), None,
+                                                          vp(out), t, m, n, n_out, CLIP, nat.QO_BF16, nat.QO_BF16, vp(ws), need, sp))
+                else:
+                    nat.check(lib.qo_w4a4_linear(vp(x), k, vp(left), vp(right), vp(wps[i % nw]), vp(sw), None, vp(out), t, m, n, n_out,
+                                                 CLIP, nat.QO_BF16, nat.QO_BF16, vp(ws), need, sp))
 
-            desc = {"workload": f"w4a4_linear (quantize + packed int4 GEMM) {t} tokens, 14336 -> 4096, bf16 in / out",
+            desc = {"workload": f"w4a4_linear{' with weights kept as int8' if args.prepared else ''} (quantize + packed int4 GEMM) {t} tokens, 14336 -> 4096, bf16 in / out",
                     "l2": f"weights rotate over {nw} buffers ({nw * n_out * k // 2 // 10**6} MB) > L2"}
         metric, unit, scale_value = "int4_matmul_TOPs", "TOP/s", lambda sec: ops / sec / 1e12
         weight_bytes = n_out * k // 2
@@ -487,6 +497,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="quantize", choices=["quantize", "quantize_wide", "gemm", "linear", "stack"])
     ap.add_argument("--tokens", type=int, default=16, help="rows of the `linear` workload")
+    ap.add_argument("--prepared", action="store_true", help="`linear`: weights also kept widened to int8 (qo_prepare_weights)")
     args = ap.parse_args()
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
         # started by hand rather than by torchrun: start one rank per GPU ourselves
