@@ -221,7 +221,7 @@ size_t qo_int4_matmul_workspace_bytes(int64_t tokens, int64_t k, int64_t n_out) 
 static int int4_matmul_impl(const int32_t* a, int64_t lda, const int32_t* b, int64_t bsk, int64_t bsn,
                             const float* sa, const float* sb, void* out, int out_dtype, int64_t t, int64_t k,
                             int64_t n, int32_t* acc_out, const void* bias, void* workspace, size_t workspace_bytes,
-                            cudaStream_t st) {
+                            cudaStream_t st, bool b_is_layer_weight = false) {
   if (t < 0 || k < 0 || n < 0) return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: negative size");
   if (k % 8) return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: k = %lld must be a multiple of 8", (long long)k);
   if (k > 262143) return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: k = %lld is beyond the supported reduction length", (long long)k);
@@ -234,7 +234,8 @@ static int int4_matmul_impl(const int32_t* a, int64_t lda, const int32_t* b, int
   // a few rows: stream the packed weights once instead of widening them for the tensor-memory kernel
   if (t_policy == 0 && gemm_skinny_supported(t, k, n, a, lda, b, bsk, bsn)) {
     t_gemm_path = 3;
-    return launch_gemm_skinny(a, lda, b, bsn, sa, sb, out, out_dtype, t, k, n, acc_out, bias, st);
+    // (b_is_layer_weight: B was not written by the kernel that precedes this one in the stream, see qo_w4a4_linear)
+    return launch_gemm_skinny(a, lda, b, bsn, sa, sb, out, out_dtype, t, k, n, acc_out, bias, st, b_is_layer_weight);
   }
   const bool fast_ok = k > 0 && gemm_sm100_supported(t, k, n, lda, bsk, bsn);
   if (t_policy == 2 && !fast_ok)
@@ -293,10 +294,12 @@ int qo_w4a4_linear(const void* x, int64_t ldx, const void* left, const void* rig
   const size_t off_gemm = off_scale + align_up((size_t)tokens * 4, 256);
   rc = qo_flatquant_quantize(x, ldx, left, right, a_packed, a_scale, tokens, m, n, clip_ratio, in_dtype, 1, QO_F32, stream);
   if (rc) return rc;
-  // weights are [n_out, k/8] with K contiguous: as the GEMM's B operand that is strides (1, k/8)
+  // weights are [n_out, k/8] with K contiguous: as the GEMM's B operand that is strides (1, k/8).  The kernel before
+  // the GEMM in the stream is this call's quantizer, which writes only the workspace, and it lets dependents start
+  // only after everything older has completed: the GEMM may fetch weights while the quantizer still runs.
   return int4_matmul_impl(a_packed, k / 8, w_packed, 1, k / 8, a_scale, w_scale, out, out_dtype, tokens, k, n_out,
                           nullptr, bias, ws + off_gemm, workspace_bytes - off_gemm,
-                          reinterpret_cast<cudaStream_t>(stream));
+                          reinterpret_cast<cudaStream_t>(stream), /*b_is_layer_weight=*/t_quant_path == 2);
 }
 
 size_t qo_prepared_weights_bytes(int64_t n_out, int64_t k) {

@@ -56,7 +56,6 @@ __global__ void __launch_bounds__(kThreads, 1)
 flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restrict__ left, const T* __restrict__ right,
                       void* __restrict__ out, void* __restrict__ scales, long long tokens, int m, int group, float clip,
                       int scale_dtype, uint32_t* __restrict__ status) {
-  grid_launch_dependents();  // a following launch of this kernel may set up its barriers and tensor memory early
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Misc* misc = reinterpret_cast<Misc*>(smem + kOffMisc);
@@ -106,6 +105,9 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
   // Programmatic dependent launch: everything above overlaps with the tail of the preceding kernel of the stream;
   // nothing below (reads of X, L, R, writes of the outputs) starts before that kernel has completed.
   grid_dependency_wait();
+  // Only now may a dependent launch start early: whatever it reads before its own wait (a following GEMM prefetches
+  // its weights) was then written by kernels that completed before this one passed the wait above.
+  grid_launch_dependents();
 
   if (warp != 0) {
     constexpr int kStagers = kThreads - 32;

@@ -23,6 +23,7 @@
 // Arithmetic as in the reference kernel (src/quant_ops/ops/quantization/int4_matmul/kernels/
 // cuda_int4_matmul_kernel.cu:49-118): int32 accumulation, then (float(acc) * scale_a[row]) * scale_b[col].
 #include "qo_internal.cuh"
+#include "sm100_ptx.cuh"
 
 namespace qo {
 namespace {
@@ -70,7 +71,8 @@ template <int NT, int RT, bool STAGED, typename OutT>
 __global__ void __launch_bounds__(kSlices * RT * 32, RT == 1 ? 2 : 1)
 int4_gemm_skinny_kernel(const uint32_t* __restrict__ a, int64_t lda, const uint32_t* __restrict__ b, int64_t ldb,
                         const float* __restrict__ sa, const float* __restrict__ sb, OutT* __restrict__ out,
-                        int32_t* __restrict__ acc_out, const OutT* __restrict__ bias, int tokens, int nchunks, int64_t n) {
+                        int32_t* __restrict__ acc_out, const OutT* __restrict__ bias, int tokens, int nchunks, int64_t n,
+                        int weights_first) {
   constexpr int kThreads = kSlices * RT * 32;
   __shared__ int red[kSlices * RT][NT][16][8 + 1];
   extern __shared__ uint4 act[];
@@ -80,14 +82,21 @@ int4_gemm_skinny_kernel(const uint32_t* __restrict__ a, int64_t lda, const uint3
   const uint4 zero4 = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);  // eight zeros per word
   const int stride4 = nchunks * 4 + 4;  // activation row stride in shared memory, in 16-byte units
 
-  if (STAGED) {
-    const int per_row = nchunks * 4, total = tokens * per_row;
-    const uint32_t base = (uint32_t)__cvta_generic_to_shared(act);
-    for (int p = threadIdx.x; p < total; p += kThreads) {
-      const int tok = p / per_row, q = p - tok * per_row;
-      cp_async16(base + (uint32_t)(tok * stride4 + q) * 16u, a + (int64_t)tok * lda + (int64_t)q * 4);
+  // Launched with programmatic stream serialization, the kernel may start while its predecessor in the stream (the
+  // activation quantizer) still runs.  weights_first: the weights are known not to come from that predecessor, so the
+  // first batch of weight loads is issued before the wait and overlaps it; everything else comes after the wait.
+  if (!weights_first) ptx::grid_dependency_wait();
+  auto stage_activations = [&]() {
+    if (STAGED) {
+      const int per_row = nchunks * 4, total = tokens * per_row;
+      const uint32_t base = (uint32_t)__cvta_generic_to_shared(act);
+      for (int p = threadIdx.x; p < total; p += kThreads) {
+        const int tok = p / per_row, q = p - tok * per_row;
+        cp_async16(base + (uint32_t)(tok * stride4 + q) * 16u, a + (int64_t)tok * lda + (int64_t)q * 4);
+      }
     }
-  }
+  };
+  if (!weights_first) stage_activations();
 
   const int per = (nchunks + kSlices - 1) / kSlices;
   const int cb = slice * per, ce = min(nchunks, cb + per);
@@ -144,6 +153,10 @@ int4_gemm_skinny_kernel(const uint32_t* __restrict__ a, int64_t lda, const uint3
   };
 
   load(0, cb);
+  if (weights_first) {
+    ptx::grid_dependency_wait();
+    stage_activations();
+  }
   if (STAGED) {
     cp_async_wait_all();
     __syncthreads();
@@ -182,7 +195,8 @@ int4_gemm_skinny_kernel(const uint32_t* __restrict__ a, int64_t lda, const uint3
 
 template <int NT, int RT, bool STAGED, typename OutT>
 int launch_cfg(const uint32_t* a, int64_t lda, const uint32_t* b, int64_t ldb, const float* sa, const float* sb, void* out,
-               int32_t* acc_out, const void* bias, int tokens, int nchunks, int64_t n, size_t smem, cudaStream_t stream) {
+               int32_t* acc_out, const void* bias, int tokens, int nchunks, int64_t n, size_t smem, int weights_first,
+               cudaStream_t stream) {
   auto kern = int4_gemm_skinny_kernel<NT, RT, STAGED, OutT>;
   if (smem > 0) {
     int dev = 0;
@@ -194,28 +208,38 @@ int launch_cfg(const uint32_t* a, int64_t lda, const uint32_t* b, int64_t ldb, c
     }
   }
   const unsigned grid = (unsigned)((n + 16 * RT - 1) / (16 * RT));
-  kern<<<grid, kSlices * RT * 32, smem, stream>>>(a, lda, b, ldb, sa, sb, reinterpret_cast<OutT*>(out), acc_out,
-                                                  reinterpret_cast<const OutT*>(bias), tokens, nchunks, n);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kSlices * RT * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  QO_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, a, lda, b, ldb, sa, sb, reinterpret_cast<OutT*>(out), acc_out,
+                                 reinterpret_cast<const OutT*>(bias), tokens, nchunks, n, weights_first));
   return check_launch("int4_gemm_skinny_kernel");
 }
 
 template <int NT, typename OutT>
 int launch_nt(const uint32_t* a, int64_t lda, const uint32_t* b, int64_t ldb, const float* sa, const float* sb, void* out,
-              int32_t* acc_out, const void* bias, int tokens, int nchunks, int64_t n, cudaStream_t stream) {
+              int32_t* acc_out, const void* bias, int tokens, int nchunks, int64_t n, int weights_first, cudaStream_t stream) {
   const size_t stage = (size_t)tokens * ((size_t)nchunks * 64 + 64);
   if (stage <= 92 * 1024)  // two CTAs of 16 channels per SM
-    return launch_cfg<NT, 1, true, OutT>(a, lda, b, ldb, sa, sb, out, acc_out, bias, tokens, nchunks, n, stage, stream);
+    return launch_cfg<NT, 1, true, OutT>(a, lda, b, ldb, sa, sb, out, acc_out, bias, tokens, nchunks, n, stage, weights_first, stream);
   if (stage <= 200 * 1024)  // one CTA of 32 channels per SM shares the copy
-    return launch_cfg<NT, 2, true, OutT>(a, lda, b, ldb, sa, sb, out, acc_out, bias, tokens, nchunks, n, stage, stream);
-  return launch_cfg<NT, 1, false, OutT>(a, lda, b, ldb, sa, sb, out, acc_out, bias, tokens, nchunks, n, 0, stream);
+    return launch_cfg<NT, 2, true, OutT>(a, lda, b, ldb, sa, sb, out, acc_out, bias, tokens, nchunks, n, stage, weights_first, stream);
+  return launch_cfg<NT, 1, false, OutT>(a, lda, b, ldb, sa, sb, out, acc_out, bias, tokens, nchunks, n, 0, weights_first, stream);
 }
 
 template <typename OutT>
 int launch_t(const uint32_t* a, int64_t lda, const uint32_t* b, int64_t ldb, const float* sa, const float* sb, void* out,
-             int32_t* acc_out, const void* bias, int tokens, int nchunks, int64_t n, cudaStream_t stream) {
-  if (tokens <= 8) return launch_nt<1, OutT>(a, lda, b, ldb, sa, sb, out, acc_out, bias, tokens, nchunks, n, stream);
-  if (tokens <= 16) return launch_nt<2, OutT>(a, lda, b, ldb, sa, sb, out, acc_out, bias, tokens, nchunks, n, stream);
-  return launch_nt<4, OutT>(a, lda, b, ldb, sa, sb, out, acc_out, bias, tokens, nchunks, n, stream);
+             int32_t* acc_out, const void* bias, int tokens, int nchunks, int64_t n, int weights_first, cudaStream_t stream) {
+  if (tokens <= 8) return launch_nt<1, OutT>(a, lda, b, ldb, sa, sb, out, acc_out, bias, tokens, nchunks, n, weights_first, stream);
+  if (tokens <= 16) return launch_nt<2, OutT>(a, lda, b, ldb, sa, sb, out, acc_out, bias, tokens, nchunks, n, weights_first, stream);
+  return launch_nt<4, OutT>(a, lda, b, ldb, sa, sb, out, acc_out, bias, tokens, nchunks, n, weights_first, stream);
 }
 
 }  // namespace
@@ -227,12 +251,13 @@ bool gemm_skinny_supported(int64_t t, int64_t k, int64_t n, const void* a, int64
 }
 
 int launch_gemm_skinny(const int32_t* a, int64_t lda, const int32_t* b, int64_t bsn, const float* sa, const float* sb, void* out,
-                       int out_dtype, int64_t t, int64_t k, int64_t n, int32_t* acc_out, const void* bias, cudaStream_t stream) {
+                       int out_dtype, int64_t t, int64_t k, int64_t n, int32_t* acc_out, const void* bias, cudaStream_t stream,
+                       bool weights_first) {
   const uint32_t* ua = reinterpret_cast<const uint32_t*>(a);
   const uint32_t* ub = reinterpret_cast<const uint32_t*>(b);
   const int nchunks = (int)(k / 128);
-  if (out_dtype == QO_F16) return launch_t<__half>(ua, lda, ub, bsn, sa, sb, out, acc_out, bias, (int)t, nchunks, n, stream);
-  if (out_dtype == QO_BF16) return launch_t<__nv_bfloat16>(ua, lda, ub, bsn, sa, sb, out, acc_out, bias, (int)t, nchunks, n, stream);
+  if (out_dtype == QO_F16) return launch_t<__half>(ua, lda, ub, bsn, sa, sb, out, acc_out, bias, (int)t, nchunks, n, weights_first ? 1 : 0, stream);
+  if (out_dtype == QO_BF16) return launch_t<__nv_bfloat16>(ua, lda, ub, bsn, sa, sb, out, acc_out, bias, (int)t, nchunks, n, weights_first ? 1 : 0, stream);
   return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: out_dtype must be QO_F16 or QO_BF16");
 }
 
