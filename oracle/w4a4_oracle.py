@@ -213,3 +213,34 @@ def quantize_weights(w: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
     s = np.maximum(np.abs(w).max(axis=1) / np.float32(7.0), np.float32(1e-8)).astype(np.float32)
     q = np.clip(np.rint(w / s[:, None]), -8, 7).astype(np.int8)
     return q, s
+
+
+# --------------------------------------------------------------------------- float simulation of the layer
+def fake_quant_linear(x, left, right, clip_ratio, w_int8, w_scale, dtype="bf16", bias=None) -> np.ndarray:
+    """Float simulation of the W4A4 layer: a second, independent statement of its intended numerics.
+
+    Restates AscendW4A4FlatQuantDynamicFakeLinearMethod.apply (w4a4_flatquant_dynamic.py:440-507) with its own
+    scale rule (get_scale_zero, :401-423): the row extremes are first widened to include 0 (xmax >= 0, xmin <= 0),
+    multiplied by clip_ratio, scale = max(|xmin|, xmax) / 7 clamped below at 1e-8; activations are quantized and
+    de-quantized in the activation dtype, the int8 weights are de-quantized with their per-channel scale and cast
+    to the activation dtype, and the product is an ordinary linear layer in that dtype.  It differs from the
+    integer path by the dtype roundings of the de-quantized operands, so it is compared with a tolerance.
+    Returns float32 holding `dtype` values, shape [tokens, n_out].
+    """
+    z = kronecker_transform(x, left, right, dtype)
+    c = np.float32(clip_ratio)
+    zmax = np.maximum(z.max(axis=1, keepdims=True), np.float32(0))
+    zmin = np.minimum(z.min(axis=1, keepdims=True), np.float32(0))
+    zmax = round_to(zmax * c, dtype)
+    zmin = round_to(zmin * c, dtype)
+    top = np.maximum(np.abs(zmin), zmax)
+    scale = np.maximum(round_to(top / np.float32(7.0), dtype), round_to(np.float32(1e-8), dtype)).astype(np.float32)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        q = round_to(z / scale, dtype)
+    q = np.clip(np.rint(np.where(np.isnan(q), np.float32(0), q)), -8, 7).astype(np.float32)
+    x_deq = round_to(q * scale, dtype)
+    w_deq = round_to(np.asarray(w_int8, dtype=np.float32) * np.asarray(w_scale, dtype=np.float32).reshape(-1, 1), dtype)
+    out = round_to(x_deq @ w_deq.T, dtype)
+    if bias is not None:
+        out = round_to(out + np.asarray(bias, dtype=np.float32).reshape(1, -1), dtype)
+    return out

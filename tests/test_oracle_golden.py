@@ -127,3 +127,20 @@ def test_torch_port_matmul_matches_reference():
     g = golden("gemm_64x512x96")
     out = torch_port.matmul(*(torch.from_numpy(g[k]) for k in ("a_packed", "b_packed", "scale_a", "scale_b")))
     np.testing.assert_array_equal(out.float().numpy(), bits_to_f32(g["out_bits"], "fp16"))
+
+
+def test_float_simulation_of_the_layer_agrees_with_the_integer_path():
+    """The reference's fake-quant layer (restated in the oracle) and the integer path describe the same layer:
+    identical scales and codes for rows that straddle zero, outputs equal up to the dtype rounding of the
+    de-quantized operands."""
+    rng = np.random.default_rng(7)
+    m, n, n_out, tokens = 16, 16, 40, 24
+    x = O.round_to(rng.standard_normal((tokens, m * n)).astype(np.float32), "bf16")
+    left = O.round_to(np.linalg.qr(rng.standard_normal((m, m)))[0].astype(np.float32), "bf16")
+    right = O.round_to(np.linalg.qr(rng.standard_normal((n, n)))[0].astype(np.float32), "bf16")
+    wq, sw = O.quantize_weights((rng.standard_normal((n_out, m * n)) * 0.02).astype(np.float32))
+    exact = O.w4a4_linear(x, left, right, 0.9, O.pack_int4_to_int32(wq), sw, "bf16", "bf16")
+    sim = O.fake_quant_linear(x, left, right, 0.9, wq, sw, "bf16")
+    assert exact.shape == sim.shape == (tokens, n_out)
+    bound = 2e-2 * np.abs(exact).max(axis=1, keepdims=True)
+    assert np.all(np.abs(exact - sim) <= bound)

@@ -112,3 +112,18 @@ def test_prepared_weights_give_identical_results(tokens, k, n_out):
     y0, y1 = plain(x.to(DEV)), kept(x.to(DEV))
     assert torch.equal(y0, y1)
     assert N.lib.qo_device_status(C.c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
+
+
+def test_layer_against_the_float_simulation():
+    """End-to-end accuracy cross-check: W4A4Linear on the GPU vs the restated fake-quant layer of the reference."""
+    tokens, k, n_out = 64, 4096, 320
+    x, left, right = make_inputs(tokens, k, "bf16", 4242, True)
+    g = torch.Generator().manual_seed(11)
+    w = torch.randn(n_out, k, generator=g) * 0.02
+    wq, sw = O.quantize_weights(w.numpy())
+    layer = q.W4A4Linear(k, n_out, clip_ratio=0.9, dtype=torch.bfloat16, device=DEV)
+    layer.load_quantized(torch.from_numpy(wq), torch.from_numpy(sw), left.to(DEV), right.to(DEV))
+    y = layer(x.to(DEV)).float().cpu().numpy()
+    sim = O.fake_quant_linear(t2f(x), t2f(left), t2f(right), 0.9, wq, sw, "bf16")
+    bound = 2e-2 * np.abs(sim).max(axis=1, keepdims=True)
+    assert np.all(np.abs(y - sim) <= bound), float((np.abs(y - sim) / bound).max())
