@@ -288,6 +288,22 @@ int qo_w4a4_linear(const void* x, int64_t ldx, const void* left, const void* rig
   }
   if (workspace_bytes < need) return fail(QO_ERR_WORKSPACE, "w4a4_linear: workspace of %zu bytes, need %zu", workspace_bytes, need);
   char* ws = reinterpret_cast<char*>(workspace);
+  if (t_policy != 1 && tokens > 32 && gemm_sm100_supported(tokens, k, n_out, k / 8, 1, k / 8)) {
+    // tensor-core route: the quantizer writes int8 codes, which is the GEMM's A operand as it is; only the weights
+    // are widened.  Layout: int8 codes [tokens, k] | scales | int8 weights [n_out, k] | K-split partial sums.
+    int8_t* a8 = reinterpret_cast<int8_t*>(ws);
+    const size_t o_scale = align_up((size_t)tokens * (size_t)k, 256);
+    float* a_scale8 = reinterpret_cast<float*>(ws + o_scale);
+    const size_t o_b = o_scale + align_up((size_t)tokens * 4, 256);
+    int8_t* b8 = reinterpret_cast<int8_t*>(ws + o_b);
+    int32_t* part = gemm_k_split(tokens, k, n_out) > 1 ? reinterpret_cast<int32_t*>(ws + o_b + align_up((size_t)n_out * (size_t)k, 256)) : nullptr;
+    rc = qo_flatquant_quantize(x, ldx, left, right, a8, a_scale8, tokens, m, n, clip_ratio, in_dtype, 0, QO_F32, stream);
+    if (rc) return rc;
+    if ((rc = launch_widen_rows(w_packed, k / 8, b8, n_out, k, reinterpret_cast<cudaStream_t>(stream)))) return rc;
+    t_gemm_path = 2;
+    return launch_gemm_sm100_s8(a8, b8, a_scale8, w_scale, out, out_dtype, tokens, k, n_out, nullptr, bias,
+                                reinterpret_cast<cudaStream_t>(stream), part);
+  }
   int32_t* a_packed = reinterpret_cast<int32_t*>(ws);
   const size_t off_scale = align_up((size_t)tokens * (size_t)(k / 8) * 4, 256);
   float* a_scale = reinterpret_cast<float*>(ws + off_scale);

@@ -634,6 +634,15 @@ int launch_gemm_sm100_s8(const int8_t* a8, const int8_t* b8, const float* sa, co
 }
 
 int launch_widen_rows(const int32_t* in, int64_t ld_words, int8_t* out, int64_t rows, int64_t k, cudaStream_t stream) {
+  if ((k % 32) == 0 && (ld_words % 4) == 0 && reinterpret_cast<uintptr_t>(in) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) {
+    const WidenJob job = {reinterpret_cast<const uint32_t*>(in), reinterpret_cast<uint4*>(out), ld_words, rows, k / 32};
+    const WidenJob none = {nullptr, nullptr, 0, 0, 1};
+    int64_t blocks = (rows * (k / 32) + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (blocks < 1) blocks = 1;
+    widen_rows2_kernel<<<(int)blocks, 256, 0, stream>>>(job, none);
+    return check_launch("widen_rows2_kernel");
+  }
   const int64_t total = rows * (k / 8);
   int64_t blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
