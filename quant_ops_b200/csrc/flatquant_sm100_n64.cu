@@ -1,4 +1,4 @@
-// FlatQuant quantizer for sm_100a, right transform of size 64 (features = M x 64 with M in {16, 32, 48, 64}):
+// FlatQuant quantizer for sm_100a, right transform of size 64 (features = M x 64 with M = 16, 24, ... 64):
 // the activation-scale configuration (4096 = 64 x 64) runs here.
 //
 // One persistent CTA per SM works on groups of 2 tokens (2M <= 128 rows of 64 elements):
@@ -73,7 +73,8 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
   const uint32_t smem_base = smem_u32(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int mpad = (m + 31) & ~31;            // each copy of L^T starts on a 32-lane boundary: a warp reads one token's columns
-  const int rows_group = kGroup * m;          // X / Y rows per group (<= 128)
+  const int rows_group = kGroup * m;          // X rows per group (<= 128)
+  const int k2 = (m + 15) & ~15;              // reduction length of the second product; a token's Y rows start at c * k2
   const long long ngroups = (tokens + kGroup - 1) / kGroup;
   // Warps whose 32 tensor-memory lanes carry no row take no part: they skip their role and the barrier counts
   // below only include the others (M = 32: the upper two quadrants of both passes are idle).
@@ -167,6 +168,17 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       }
       *reinterpret_cast<uint4*>(smem + kOffLL + (r >> 3) * 1024 + (r & 7) * 128 + ((kc ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
     }
+    if (k2 != m) {
+      // M is not a multiple of 16: rows m .. k2-1 of each token's Y block only pad the reduction; they are zeroed once
+      // (the Y pass never writes them) after everybody has finished reading the raw copies that live in the Y stages
+      asm volatile("bar.sync 1, %0;" ::"n"(kStagers) : "memory");
+      const int pad_rows = k2 - m, chunks = kYStages * kGroup * pad_rows * 8;
+      for (int idx = t13; idx < chunks; idx += kStagers) {
+        const int ch = idx & 7, pr = (idx >> 3) % pad_rows, blk = (idx >> 3) / pad_rows;  // blk = stage * kGroup + token
+        const int row = (blk % kGroup) * k2 + m + pr;
+        *reinterpret_cast<uint4*>(smem + kOffY + (blk / kGroup) * kStageBytes + row * 128 + (ch << 4)) = make_uint4(0, 0, 0, 0);
+      }
+    }
     fence_proxy_async_smem();
     asm volatile("bar.sync 1, %0;" ::"n"(kStagers) : "memory");
   }
@@ -216,8 +228,8 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
     if (lane == 0) {
       const uint32_t idesc2 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 0, 1, 128, 128);
       const uint64_t desc_ll = umma_smem_desc_sw128(smem_base + kOffLL, 16, 1024);
-      const uint64_t desc_y0 = umma_smem_desc_sw128(smem_base + kOffY, (uint32_t)(m * 128), 1024);
-      const int ksteps2 = m >> 4;
+      const uint64_t desc_y0 = umma_smem_desc_sw128(smem_base + kOffY, (uint32_t)(k2 * 128), 1024);  // N blocks = tokens, k2 rows apart
+      const int ksteps2 = k2 >> 4;
       int sy = 0, phy = 0;
       for (int it = 0; it < mine; ++it) {
         const int e = it & 1, ph = (it >> 1) & 1;
@@ -255,7 +267,8 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       mbar_arrive_warp(smem_u32(&misc->d1_empty[s]));  // accumulators are in registers: the stage can be overwritten
       if (tid == kEpi1Warp0 * 32) TR(3, it, 1);
       if (r < rows_group) {
-        uint8_t* yrow = smem + kOffY + s * kStageBytes + r * 128;
+        const int yr = r < m ? r : r - m + k2;  // row of the Y stage: token c's rows start at c * k2
+        uint8_t* yrow = smem + kOffY + s * kStageBytes + yr * 128;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           uint4 w;
@@ -263,7 +276,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
           w.y = pack2<T>(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
           w.z = pack2<T>(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
           w.w = pack2<T>(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
-          *reinterpret_cast<uint4*>(yrow + (((h * 4 + j) ^ (r & 7)) << 4)) = w;
+          *reinterpret_cast<uint4*>(yrow + (((h * 4 + j) ^ (yr & 7)) << 4)) = w;
         }
       }
       fence_proxy_async_smem();
@@ -455,7 +468,7 @@ extern "C" __attribute__((visibility("default"))) int qo_debug_set_trace(long lo
 }
 #endif
 
-bool flatquant_sm100_n64_supported(int m, int n) { return n == 64 && m >= 16 && m <= 64 && (m % 16) == 0; }
+bool flatquant_sm100_n64_supported(int m, int n) { return n == 64 && m >= 16 && m <= 64 && (m % 8) == 0; }
 
 int launch_flatquant_sm100_n64(int mode, const void* x_map, const void* left, const void* right, void* out, void* scales,
                                int64_t tokens, int m, float clip, int in_dtype, int scale_dtype, uint32_t* status,

@@ -106,10 +106,11 @@ def test_right_transform_of_size_128(m, dtype, tokens, pack):
 
 
 @pytest.mark.parametrize("m,dtype,tokens,pack", [(16, "bf16", 41, True), (48, "bf16", 77, True), (48, "fp16", 6, False), (32, "bf16", 3, True),
-                                                 (56, "bf16", 100, True), (40, "bf16", 9, True), (24, "fp16", 33, False)])
+                                                 (56, "bf16", 100, True), (40, "bf16", 9, True), (24, "fp16", 33, False),
+                                                 (20, "bf16", 7, True), (36, "fp16", 50, False)])
 def test_right_transform_of_size_64_small_left(m, dtype, tokens, pack):
     """(M, 64) with M < 64, e.g. 3072 = 48 x 64: groups of two tokens whose rows do not fill whole warps; 3584 = 56 x 64
-    and other M that are not multiples of 16 take the shape-general tcgen05 kernel."""
+    and other multiples of 8 pad each token's reduction length; M = 20 or 36 take the shape-general tcgen05 kernel."""
     x, left, right = make_inputs(tokens, m * 64, dtype, 17 * m + tokens, True, mn=(m, 64))
     ref_codes, ref_scales = O.flatquant_quantize(t2f(x), t2f(left), t2f(right), 0.9, pack, dtype)
     for label, codes, scales in run_both(x, left, right, 0.9, pack, dtype):
