@@ -434,7 +434,7 @@ int qo_flatquant_quantize_host(const void* x_host, const void* left_host, const 
 
   const size_t feat = (size_t)m * n, esz = dtype_size(in_dtype), ssz = dtype_size(scale_dtype);
   const size_t code_row = pack_int32 ? feat / 2 : feat;
-  int64_t slice = (int64_t)((24u << 20) / (feat * esz));  // about 24 MB of activations per slice
+  int64_t slice = (int64_t)((8u << 20) / (feat * esz));  // about 8 MB of activations per slice: short pipeline fill and drain
   if (slice < 1) slice = 1;
   if (slice > tokens) slice = tokens;
   const size_t x_bytes = align_up((size_t)slice * feat * esz, 256), c_bytes = align_up((size_t)slice * code_row, 256),
@@ -447,7 +447,10 @@ int qo_flatquant_quantize_host(const void* x_host, const void* left_host, const 
   p += lr_bytes;
   QO_CUDA_TRY(cudaMemcpyAsync(d_left, left_host, (size_t)m * m * esz, cudaMemcpyHostToDevice, streams[dev][0]));
   QO_CUDA_TRY(cudaMemcpyAsync(d_right, right_host, (size_t)n * n * esz, cudaMemcpyHostToDevice, streams[dev][0]));
-  QO_CUDA_TRY(cudaStreamSynchronize(streams[dev][0]));
+  static cudaEvent_t lr_ready[kMaxDevices] = {};
+  if (!lr_ready[dev]) QO_CUDA_TRY(cudaEventCreateWithFlags(&lr_ready[dev], cudaEventDisableTiming));
+  QO_CUDA_TRY(cudaEventRecord(lr_ready[dev], streams[dev][0]));
+  for (int s = 1; s < kSlots; ++s) QO_CUDA_TRY(cudaStreamWaitEvent(streams[dev][s], lr_ready[dev], 0));  // the transforms are on the device
 
   int slot = 0;
   for (int64_t t0 = 0; t0 < tokens; t0 += slice, slot = (slot + 1) % kSlots) {
