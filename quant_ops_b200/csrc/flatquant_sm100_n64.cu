@@ -59,7 +59,7 @@ struct Misc {
   uint64_t d1_full[kYStages], d1_empty[kYStages], y_full[kYStages], y_empty[kYStages];
   uint64_t d2_full[2], d2_empty[2], set_sync[2];
   uint32_t tmem_base;
-  int absmax_bits[2][3][8];
+  alignas(16) float absmax_part[2][3][2][4];  // [set][use % 3][token][warp of the token]: per-warp maxima, never-written slots stay 0
 };
 
 template <typename T, int MODE>
@@ -100,7 +100,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       mbar_init(smem_u32(&misc->d2_empty[i]), 2 * nq2);  // one arrival per working warp of a quantize set
       mbar_init(smem_u32(&misc->set_sync[i]), 2 * nq2);
     }
-    for (int i = 0; i < 2 * 3 * 8; ++i) (&misc->absmax_bits[0][0][0])[i] = 0;
+    for (int i = 0; i < 2 * 3 * 2 * 4; ++i) (&misc->absmax_part[0][0][0][0])[i] = 0.f;
     fence_barrier_init();
     prefetch_tensormap(&x_map);
   }
@@ -290,7 +290,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
     const int e = (warp - kEpi2Warp0) >> 3, q = warp & 3, h = ((warp - kEpi2Warp0) >> 2) & 1, l = q * 32 + lane;
     const int c = l / mpad, mi = l - c * mpad;      // lane block c holds a copy of the Z rows: it serves token c
     const bool active = c < kGroup && mi < m;
-    constexpr bool warp_uniform = true;             // copies start on warp boundaries: all rows of a warp belong to one token
+    const int slot = ((q * 32 - c * mpad) >> 5) * 2 + h;  // this warp's index among the (at most 4) warps of its token
     const int feat = m * 64;
     long long grp = (long long)blockIdx.x + (long long)e * gridDim.x;
     const int mine_q = ((q * 32) / mpad < kGroup && q * 32 - ((q * 32) / mpad) * mpad < m) ? mine : 0;  // idle quadrants skip the pass
@@ -328,19 +328,19 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
         m0 = P2<T>::absmax(P2<T>::absmax(m0, m1), P2<T>::absmax(m2, m3));
         float amax = valid ? fmaxf(fabsf(P2<T>::lo(m0)), fabsf(P2<T>::hi(m0))) : 0.f;
         const float row_amax = amax;  // this row's own extreme, used below to skip the clamp
-        if (warp_uniform) {
-          amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(amax)));  // non-negative floats order as integers
-          if (lane == 0 && active) atomicMax(&misc->absmax_bits[e][buf][c], __float_as_int(amax));
-        } else if (active) {
-          atomicMax(&misc->absmax_bits[e][buf][c], __float_as_int(amax));
-        }
+        // every warp serves one token (copies start on warp boundaries): its maximum goes into the warp's own slot
+        amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(amax)));  // non-negative floats order as integers
+        if (lane == 0 && c < kGroup) misc->absmax_part[e][buf][c][slot] = amax;
         // the 128 threads of the set meet here (bounded); afterwards the slot holds the token's absmax
         const uint32_t gs = smem_u32(&misc->set_sync[e]);
         mbar_arrive_warp(gs);
         if (!__all_sync(0xffffffffu, mbar_wait(gs, ph))) { atomicCAS(status, 0u, 0x810u + e); break; }
         if (lane == 0 && q == 2 && h == 0) TR(4 + e, use, 2);
-        if (active) amax = __int_as_float(misc->absmax_bits[e][buf][c]);
-        if (l < 8) misc->absmax_bits[e][(use + 2) % 3][l] = 0;
+        {
+          // the slot buffer of this use is next written three uses later, after two more passes of this barrier
+          const float4 p4 = *reinterpret_cast<const float4*>(&misc->absmax_part[e][buf][c < kGroup ? c : 0][0]);
+          amax = fmaxf(fmaxf(p4.x, p4.y), fmaxf(p4.z, p4.w));
+        }
         // max of the rounded values = rounded max; clip * absmax and the division by 7 are rounded like the reference.
         // top / 7 can neither hit nor come within 2^-13 (relative) of a midpoint of the 16-bit format, so the
         // float32 product with 1/7 rounds to the same 16-bit value as the exact quotient.
