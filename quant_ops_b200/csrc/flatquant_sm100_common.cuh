@@ -212,11 +212,12 @@ int launch_flatquant_sm100_n64(int mode, const void* x_map, const void* left, co
                                int64_t tokens, int m, float clip, int in_dtype, int scale_dtype, uint32_t* status,
                                cudaStream_t stream);
 
-// one launch of the N = 128 kernel (flatquant_sm100_n128.cu); tiles of flatquant_sm100_n128_group(m) tokens
+// one launch of the kernel for right transforms of 80 .. 128 (flatquant_sm100_n128.cu); tiles of
+// flatquant_sm100_n128_group(m) tokens
 bool flatquant_sm100_n128_supported(int m, int n);
 int flatquant_sm100_n128_group(int m);
 int launch_flatquant_sm100_n128(int mode, const void* x_map, const void* left, const void* right, void* out, void* scales,
-                                int64_t tokens, int m, float clip, int in_dtype, int scale_dtype, uint32_t* status,
+                                int64_t tokens, int m, int n, float clip, int in_dtype, int scale_dtype, uint32_t* status,
                                 cudaStream_t stream);
 
 }  // namespace qo

@@ -1,5 +1,7 @@
-// FlatQuant quantizer for sm_100a, right transform of size 128 (features = M x 128, 16 <= M <= 128): the hidden sizes
-// 14336 = 112 x 128, 11008 = 86 x 128 and 8192 = 64 x 128 run here.
+// FlatQuant quantizer for sm_100a, right transform of size 80, 96, 112 or 128 (features = M x N, 16 <= M <= 128): the
+// hidden sizes 14336 = 112 x 128, 11008 = 86 x 128, 8192 = 64 x 128, 7168 = 64 x 112, 6144 = 64 x 96, 5120 = 64 x 80
+// run here.  For N < 128 everything is laid out as for N = 128: the TMA fills the missing columns of X with zeros,
+// R^T is staged with zero rows and columns, so the extra columns of Y and Z are exact zeros; they are not stored.
 //
 // One persistent CTA per SM works on tiles of G tokens: G = 2 when M <= 64 and M is a multiple of 16, else G = 1.
 //
@@ -51,10 +53,21 @@ struct Misc {
   int absmax_bits[3][2];
 };
 
+// the packed words of up to 32 codes (`cols` of them real, a multiple of 16): one 16-byte store when all four words are
+// real and the address allows it, else 8 bytes at a time (N = 80, 112: rows are only 8-byte aligned)
+__device__ __forceinline__ void store_words(uint32_t* dst, const uint32_t (&w)[4], int cols) {
+  if (cols == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+    *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+  } else {
+    *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+    if (cols == 32) *reinterpret_cast<uint2*>(dst + 2) = make_uint2(w[2], w[3]);
+  }
+}
+
 template <typename T, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restrict__ left, const T* __restrict__ right,
-                      void* __restrict__ out, void* __restrict__ scales, long long tokens, int m, int group, float clip,
+                      void* __restrict__ out, void* __restrict__ scales, long long tokens, int m, int nc, int group, float clip,
                       int scale_dtype, uint32_t* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -74,6 +87,7 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
     const int cc = (qq * 32) / mpad32;
     nq2 += (cc < group && qq * 32 - cc * mpad32 < m) ? 1 : 0;
   }
+  const int nh2 = (nc + 31) >> 5;             // 32-column blocks of Z that hold real columns (quantize-pass warps per quadrant)
   int mine = 0;                               // tiles this CTA works on
   if ((long long)blockIdx.x < ntiles) mine = (int)((ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x);
 
@@ -87,9 +101,9 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&misc->d2_full[i]), 1);
-      mbar_init(smem_u32(&misc->d2_empty[i]), 4 * nq2);  // one arrival per working warp of the quantize pass
+      mbar_init(smem_u32(&misc->d2_empty[i]), nh2 * nq2);  // one arrival per working warp of the quantize pass
     }
-    mbar_init(smem_u32(&misc->set_sync), 4 * nq2);
+    mbar_init(smem_u32(&misc->set_sync), nh2 * nq2);
     for (int i = 0; i < 3 * 2; ++i) (&misc->absmax_bits[0][0])[i] = 0;
     fence_barrier_init();
     prefetch_tensormap(&x_map);
@@ -116,7 +130,7 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
     uint16_t* raw_l = reinterpret_cast<uint16_t*>(smem + kOffY);
     uint16_t* raw_r = reinterpret_cast<uint16_t*>(smem + kOffY + kStageBytes);
     {
-      const int l_chunks = (m * m) / 8, r_chunks = 128 * 128 / 8;
+      const int l_chunks = (m * m) / 8, r_chunks = nc * nc / 8;
       constexpr int kMaxIter = (2 * 128 * 128 / 8 + kStagers - 1) / kStagers;
       uint4 tmp[kMaxIter];
 #pragma unroll
@@ -138,10 +152,12 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
     // 2-byte reads of a warp are contiguous and each thread makes one 16-byte swizzled store.
     for (int idx = t13; idx < 128 * 16; idx += kStagers) {
       const int n = idx & 127, jc = idx >> 7;
-      uint32_t w[4];
+      uint32_t w[4] = {0, 0, 0, 0};  // rows and columns past N stay zero
+      if (n < nc && 8 * jc < nc) {
 #pragma unroll
-      for (int e2 = 0; e2 < 4; ++e2)
-        w[e2] = (uint32_t)raw_r[(8 * jc + 2 * e2) * 128 + n] | ((uint32_t)raw_r[(8 * jc + 2 * e2 + 1) * 128 + n] << 16);
+        for (int e2 = 0; e2 < 4; ++e2)
+          w[e2] = (uint32_t)raw_r[(8 * jc + 2 * e2) * nc + n] | ((uint32_t)raw_r[(8 * jc + 2 * e2 + 1) * nc + n] << 16);
+      }
       *reinterpret_cast<uint4*>(smem + kOffR + (jc >> 3) * kAtomBytes + (n >> 3) * 1024 + (n & 7) * 128 + (((jc & 7) ^ (n & 7)) << 4)) =
           make_uint4(w[0], w[1], w[2], w[3]);
     }
@@ -193,8 +209,8 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
         }
         tc_fence_after();
         const uint64_t da = desc_x0 + (uint64_t)(sx * (kStageBytes >> 4));
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
+#pragma unroll 1
+        for (int ks = 0; ks < (nc >> 4); ++ks) {
           const uint64_t off = (uint64_t)((ks >> 2) * (kAtomBytes >> 4) + (ks & 3) * 2);  // K atom, then 32 bytes per step
           mma_f16_ss(tmem + s1 * 128, da + off, desc_r + off, idesc1, ks);
         }
@@ -206,7 +222,7 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
     }
   } else if (warp == 2) {
     if (lane == 0) {
-      const uint32_t idesc2 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 0, 1, 128, group == 2 ? 256 : 128);
+      const uint32_t idesc2 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 0, 1, 128, group == 2 ? 256 : nc);
       const uint64_t desc_ll = umma_smem_desc_sw128(smem_base + kOffLL, 16, 1024);
       // N-major B operand: the stride between 64-column blocks along N is m rows (G = 2: token blocks interleave
       // with the column halves) or one atom (G = 1)
@@ -276,13 +292,14 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
     const int c = l / mpad, mi = l - c * mpad;  // lane block c holds the Z rows of token c (copies start on warp boundaries)
     const bool active = c < group && mi < m;
     constexpr bool warp_uniform = true;         // all rows of a warp belong to one token
-    const int feat = m * 128;
+    const int feat = m * nc;
     const int c0 = h * 32;
+    const int cols = min(32, max(0, nc - c0));  // real columns among this warp's 32 (a multiple of 16)
     // G = 1: two accumulator stages of 128 columns, natural column order.  G = 2: one stage of 256 columns whose
     // 64-column blocks are ordered (half 0, token 0), (half 0, token 1), (half 1, token 0), (half 1, token 1).
     const uint32_t col_in_stage = group == 2 ? (uint32_t)((((h >> 1) * 2 + (active ? c : 0)) * 64) + (h & 1) * 32) : (uint32_t)c0;
     long long tile = blockIdx.x;
-    const bool warp_works = (q * 32) / mpad < group && q * 32 - ((q * 32) / mpad) * mpad < m;
+    const bool warp_works = (q * 32) / mpad < group && q * 32 - ((q * 32) / mpad) * mpad < m && cols > 0;
     for (int it = 0; it < (warp_works ? mine : 0); ++it, tile += gridDim.x) {
       const int e = group == 2 ? 0 : (it & 1), use = group == 2 ? it : (it >> 1);
       const int buf = it % 3;
@@ -295,13 +312,19 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive_warp(smem_u32(&misc->d2_empty[e]));  // the Z accumulators of this stage are free again
+      if (cols < 32) {
+        // N = 80 or 112: the upper 16 columns of this block were not written by the second product (its N is the
+        // real width when a tile is one token); they must not reach the absmax
+#pragma unroll
+        for (int j = 16; j < 32; ++j) v[j] = 0u;
+      }
 
       if (MODE == kTransform) {
         if (valid) {
-          float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + tok * feat + mi * 128 + c0);
+          float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + tok * feat + mi * nc + c0);
 #pragma unroll
           for (int j = 0; j < 8; ++j)
-            dst[j] = make_float4(DT<T>::rnd(__uint_as_float(v[4 * j])), DT<T>::rnd(__uint_as_float(v[4 * j + 1])),
+            if (4 * j < cols) dst[j] = make_float4(DT<T>::rnd(__uint_as_float(v[4 * j])), DT<T>::rnd(__uint_as_float(v[4 * j + 1])),
                                  DT<T>::rnd(__uint_as_float(v[4 * j + 2])), DT<T>::rnd(__uint_as_float(v[4 * j + 3])));
         }
         continue;
@@ -356,10 +379,7 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
 #pragma unroll
           for (int j = 0; j < 4; ++j) w[j] = quantize8<T, false>(&zz[4 * j], s, inv_s, rhi2, rlo2);
         }
-        if (valid) {
-          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(out) + tok * (feat / 8) + (mi * 128 + c0) / 8);
-          *dst = make_uint4(w[0], w[1], w[2], w[3]);
-        }
+        if (valid) store_words(reinterpret_cast<uint32_t*>(out) + tok * (feat / 8) + (mi * nc + c0) / 8, w, cols);
       } else {
         uint32_t pb[4], qb[4];
         if (!zero_scale) {
@@ -381,13 +401,13 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
         }
         if (MODE == kPacked) {
           if (valid) {
-            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(out) + tok * (feat / 8) + (mi * 128 + c0) / 8);
-            *dst = make_uint4(pack8(pb[0], qb[0]), pack8(pb[1], qb[1]), pack8(pb[2], qb[2]), pack8(pb[3], qb[3]));
+            const uint32_t w[4] = {pack8(pb[0], qb[0]), pack8(pb[1], qb[1]), pack8(pb[2], qb[2]), pack8(pb[3], qb[3])};
+            store_words(reinterpret_cast<uint32_t*>(out) + tok * (feat / 8) + (mi * nc + c0) / 8, w, cols);
           }
         } else if (valid) {
-          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<int8_t*>(out) + tok * feat + mi * 128 + c0);
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<int8_t*>(out) + tok * feat + mi * nc + c0);  // 16-byte aligned: N % 16 == 0
           dst[0] = make_uint4(bytes4(pb[0]), bytes4(qb[0]), bytes4(pb[1]), bytes4(qb[1]));
-          dst[1] = make_uint4(bytes4(pb[2]), bytes4(qb[2]), bytes4(pb[3]), bytes4(qb[3]));
+          if (cols > 16) dst[1] = make_uint4(bytes4(pb[2]), bytes4(qb[2]), bytes4(pb[3]), bytes4(qb[3]));
         }
       }
     }
@@ -403,7 +423,7 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
 
 template <typename T, int MODE>
 int launch_one(const CUtensorMap& map, const void* left, const void* right, void* out, void* scales, int64_t tokens, int m,
-               float clip, int scale_dtype, uint32_t* status, cudaStream_t stream) {
+               int nc, float clip, int scale_dtype, uint32_t* status, cudaStream_t stream) {
   auto kern = flatquant_n128_kernel<T, MODE>;
   int dev = 0, sms = 148;
   QO_CUDA_TRY(cudaGetDevice(&dev));
@@ -427,32 +447,32 @@ int launch_one(const CUtensorMap& map, const void* left, const void* right, void
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   QO_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, map, reinterpret_cast<const T*>(left), reinterpret_cast<const T*>(right), out, scales,
-                                 (long long)tokens, m, group, clip, scale_dtype, status));
+                                 (long long)tokens, m, nc, group, clip, scale_dtype, status));
   return check_launch("flatquant_n128_kernel");
 }
 
 template <typename T>
 int launch_mode(int mode, const CUtensorMap& map, const void* left, const void* right, void* out, void* scales,
-                int64_t tokens, int m, float clip, int scale_dtype, uint32_t* status, cudaStream_t stream) {
+                int64_t tokens, int m, int nc, float clip, int scale_dtype, uint32_t* status, cudaStream_t stream) {
   switch (mode) {
-    case kInt8: return launch_one<T, kInt8>(map, left, right, out, scales, tokens, m, clip, scale_dtype, status, stream);
-    case kPacked: return launch_one<T, kPacked>(map, left, right, out, scales, tokens, m, clip, scale_dtype, status, stream);
-    default: return launch_one<T, kTransform>(map, left, right, out, scales, tokens, m, clip, scale_dtype, status, stream);
+    case kInt8: return launch_one<T, kInt8>(map, left, right, out, scales, tokens, m, nc, clip, scale_dtype, status, stream);
+    case kPacked: return launch_one<T, kPacked>(map, left, right, out, scales, tokens, m, nc, clip, scale_dtype, status, stream);
+    default: return launch_one<T, kTransform>(map, left, right, out, scales, tokens, m, nc, clip, scale_dtype, status, stream);
   }
 }
 
 }  // namespace
 
-bool flatquant_sm100_n128_supported(int m, int n) { return n == 128 && m >= 16 && m <= 128; }
+bool flatquant_sm100_n128_supported(int m, int n) { return n > 64 && n <= 128 && (n % 16) == 0 && m >= 16 && m <= 128; }
 int flatquant_sm100_n128_group(int m) { return (m <= 64 && (m % 16) == 0) ? 2 : 1; }
 
 int launch_flatquant_sm100_n128(int mode, const void* x_map, const void* left, const void* right, void* out, void* scales,
-                                int64_t tokens, int m, float clip, int in_dtype, int scale_dtype, uint32_t* status,
+                                int64_t tokens, int m, int n, float clip, int in_dtype, int scale_dtype, uint32_t* status,
                                 cudaStream_t stream) {
   const CUtensorMap& map = *reinterpret_cast<const CUtensorMap*>(x_map);
   if (in_dtype == QO_BF16)
-    return launch_mode<__nv_bfloat16>(mode, map, left, right, out, scales, tokens, m, clip, scale_dtype, status, stream);
-  return launch_mode<__half>(mode, map, left, right, out, scales, tokens, m, clip, scale_dtype, status, stream);
+    return launch_mode<__nv_bfloat16>(mode, map, left, right, out, scales, tokens, m, n, clip, scale_dtype, status, stream);
+  return launch_mode<__half>(mode, map, left, right, out, scales, tokens, m, n, clip, scale_dtype, status, stream);
 }
 
 }  // namespace qo
