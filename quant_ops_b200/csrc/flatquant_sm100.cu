@@ -503,7 +503,7 @@ bool flatquant_sm100_supported(int64_t ldx, int m, int n, int in_dtype, const vo
                                float clip) {
   if (in_dtype != QO_F16 && in_dtype != QO_BF16) return false;
   if (!(clip > 0.f)) return false;                            // the single running absmax needs a positive clip ratio
-  if (n != 64 && !flatquant_sm100_n128_supported(m, n)) return false;  // right transform of 64, or 80 / 96 / 112 / 128
+  if (n != 64 && !flatquant_sm100_n128_supported(m, n) && !flatquant_sm100_n64_supported(m, n)) return false;
   if (m < 16 || m > 128) return false;
   if (ldx % 8) return false;                                  // TMA: row stride must be a multiple of 16 bytes
   if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(left) % 16 || reinterpret_cast<uintptr_t>(right) % 16) return false;
@@ -535,7 +535,7 @@ int launch_flatquant_sm100_mode(int mode, const void* x, int64_t ldx, const void
   if (r != CUDA_SUCCESS) return fail(QO_ERR_CUDA, "flatquant: cuTensorMapEncodeTiled failed with code %d", (int)r);
 
   if (batched)
-    return launch_flatquant_sm100_n64(mode, &map, left, right, codes, scales, tokens, m, clip, in_dtype, scale_dtype, status, stream);
+    return launch_flatquant_sm100_n64(mode, &map, left, right, codes, scales, tokens, m, n, clip, in_dtype, scale_dtype, status, stream);
   if (wide)
     return launch_flatquant_sm100_n128(mode, &map, left, right, codes, scales, tokens, m, n, clip, in_dtype, scale_dtype, status, stream);
   if (in_dtype == QO_BF16)

@@ -204,12 +204,23 @@ __device__ __forceinline__ uint32_t pack8(uint32_t p, uint32_t q) {
 // 4 nibble-bytes (offset binary) -> 4 signed bytes
 __device__ __forceinline__ uint32_t bytes4(uint32_t p) { return ((p | 0x80808080u) - 0x08080808u) ^ 0x80808080u; }
 
+// the packed words of up to 32 codes (`cols` of them real, a multiple of 16): one 16-byte store when all four words are
+// real and the address allows it, else 8 bytes at a time (rows of 16, 48, 80 or 112 codes are only 8-byte aligned)
+__device__ __forceinline__ void store_words(uint32_t* dst, const uint32_t (&w)[4], int cols) {
+  if (cols == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+    *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+  } else {
+    *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+    if (cols == 32) *reinterpret_cast<uint2*>(dst + 2) = make_uint2(w[2], w[3]);
+  }
+}
+
 }  // namespace fq
 
 // one launch of the batched N = 64 kernel (flatquant_sm100_n64.cu); same contract as launch_flatquant_sm100_mode
 bool flatquant_sm100_n64_supported(int m, int n);
 int launch_flatquant_sm100_n64(int mode, const void* x_map, const void* left, const void* right, void* out, void* scales,
-                               int64_t tokens, int m, float clip, int in_dtype, int scale_dtype, uint32_t* status,
+                               int64_t tokens, int m, int n, float clip, int in_dtype, int scale_dtype, uint32_t* status,
                                cudaStream_t stream);
 
 // one launch of the kernel for right transforms of 80 .. 128 (flatquant_sm100_n128.cu); tiles of

@@ -53,22 +53,13 @@ struct Misc {
   int absmax_bits[3][2];
 };
 
-// the packed words of up to 32 codes (`cols` of them real, a multiple of 16): one 16-byte store when all four words are
-// real and the address allows it, else 8 bytes at a time (N = 80, 112: rows are only 8-byte aligned)
-__device__ __forceinline__ void store_words(uint32_t* dst, const uint32_t (&w)[4], int cols) {
-  if (cols == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-    *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
-  } else {
-    *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
-    if (cols == 32) *reinterpret_cast<uint2*>(dst + 2) = make_uint2(w[2], w[3]);
-  }
-}
-
-template <typename T, int MODE>
+// FULL: the right transform is 128 wide (compile-time widths keep the common shapes free of the narrow-case tests)
+template <typename T, int MODE, bool FULL>
 __global__ void __launch_bounds__(kThreads, 1)
 flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restrict__ left, const T* __restrict__ right,
-                      void* __restrict__ out, void* __restrict__ scales, long long tokens, int m, int nc, int group, float clip,
+                      void* __restrict__ out, void* __restrict__ scales, long long tokens, int m, int nc_arg, int group, float clip,
                       int scale_dtype, uint32_t* __restrict__ status) {
+  const int nc = FULL ? 128 : nc_arg;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Misc* misc = reinterpret_cast<Misc*>(smem + kOffMisc);
@@ -209,10 +200,18 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
         }
         tc_fence_after();
         const uint64_t da = desc_x0 + (uint64_t)(sx * (kStageBytes >> 4));
+        if (FULL) {
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint64_t off = (uint64_t)((ks >> 2) * (kAtomBytes >> 4) + (ks & 3) * 2);  // K atom, then 32 bytes per step
+            mma_f16_ss(tmem + s1 * 128, da + off, desc_r + off, idesc1, ks);
+          }
+        } else {
 #pragma unroll 1
-        for (int ks = 0; ks < (nc >> 4); ++ks) {
-          const uint64_t off = (uint64_t)((ks >> 2) * (kAtomBytes >> 4) + (ks & 3) * 2);  // K atom, then 32 bytes per step
-          mma_f16_ss(tmem + s1 * 128, da + off, desc_r + off, idesc1, ks);
+          for (int ks = 0; ks < (nc >> 4); ++ks) {
+            const uint64_t off = (uint64_t)((ks >> 2) * (kAtomBytes >> 4) + (ks & 3) * 2);
+            mma_f16_ss(tmem + s1 * 128, da + off, desc_r + off, idesc1, ks);
+          }
         }
         mma_commit(smem_u32(&misc->empty_x[sx]));
         mma_commit(smem_u32(&misc->d1_full[s1]));
@@ -294,7 +293,7 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
     constexpr bool warp_uniform = true;         // all rows of a warp belong to one token
     const int feat = m * nc;
     const int c0 = h * 32;
-    const int cols = min(32, max(0, nc - c0));  // real columns among this warp's 32 (a multiple of 16)
+    const int cols = FULL ? 32 : min(32, max(0, nc - c0));  // real columns among this warp's 32 (a multiple of 16)
     // G = 1: two accumulator stages of 128 columns, natural column order.  G = 2: one stage of 256 columns whose
     // 64-column blocks are ordered (half 0, token 0), (half 0, token 1), (half 1, token 0), (half 1, token 1).
     const uint32_t col_in_stage = group == 2 ? (uint32_t)((((h >> 1) * 2 + (active ? c : 0)) * 64) + (h & 1) * 32) : (uint32_t)c0;
@@ -421,10 +420,10 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
   }
 }
 
-template <typename T, int MODE>
+template <typename T, int MODE, bool FULL>
 int launch_one(const CUtensorMap& map, const void* left, const void* right, void* out, void* scales, int64_t tokens, int m,
                int nc, float clip, int scale_dtype, uint32_t* status, cudaStream_t stream) {
-  auto kern = flatquant_n128_kernel<T, MODE>;
+  auto kern = flatquant_n128_kernel<T, MODE, FULL>;
   int dev = 0, sms = 148;
   QO_CUDA_TRY(cudaGetDevice(&dev));
   static bool configured[64] = {};
@@ -454,10 +453,17 @@ int launch_one(const CUtensorMap& map, const void* left, const void* right, void
 template <typename T>
 int launch_mode(int mode, const CUtensorMap& map, const void* left, const void* right, void* out, void* scales,
                 int64_t tokens, int m, int nc, float clip, int scale_dtype, uint32_t* status, cudaStream_t stream) {
+  if (nc == 128) {
+    switch (mode) {
+      case kInt8: return launch_one<T, kInt8, true>(map, left, right, out, scales, tokens, m, nc, clip, scale_dtype, status, stream);
+      case kPacked: return launch_one<T, kPacked, true>(map, left, right, out, scales, tokens, m, nc, clip, scale_dtype, status, stream);
+      default: return launch_one<T, kTransform, true>(map, left, right, out, scales, tokens, m, nc, clip, scale_dtype, status, stream);
+    }
+  }
   switch (mode) {
-    case kInt8: return launch_one<T, kInt8>(map, left, right, out, scales, tokens, m, nc, clip, scale_dtype, status, stream);
-    case kPacked: return launch_one<T, kPacked>(map, left, right, out, scales, tokens, m, nc, clip, scale_dtype, status, stream);
-    default: return launch_one<T, kTransform>(map, left, right, out, scales, tokens, m, nc, clip, scale_dtype, status, stream);
+    case kInt8: return launch_one<T, kInt8, false>(map, left, right, out, scales, tokens, m, nc, clip, scale_dtype, status, stream);
+    case kPacked: return launch_one<T, kPacked, false>(map, left, right, out, scales, tokens, m, nc, clip, scale_dtype, status, stream);
+    default: return launch_one<T, kTransform, false>(map, left, right, out, scales, tokens, m, nc, clip, scale_dtype, status, stream);
   }
 }
 

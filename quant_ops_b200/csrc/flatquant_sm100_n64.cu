@@ -1,5 +1,7 @@
 // FlatQuant quantizer for sm_100a, right transform of size 64 (features = M x 64 with M = 16, 24, ... 64):
-// the activation-scale configuration (4096 = 64 x 64) runs here.
+// the activation-scale configuration (4096 = 64 x 64) runs here.  Right transforms of 16, 32 and 48 (1024 = 32 x 32,
+// 1536 = 32 x 48, 256 = 16 x 16) use the same layout: the TMA fills the missing columns of X with zeros, R^T is staged
+// with zero rows and columns, so the extra columns of Y and Z are exact zeros; they are not stored.
 //
 // One persistent CTA per SM works on groups of 2 tokens (2M <= 128 rows of 64 elements):
 //
@@ -62,11 +64,13 @@ struct Misc {
   alignas(16) float absmax_part[2][3][2][4];  // [set][use % 3][token][warp of the token]: per-warp maxima, never-written slots stay 0
 };
 
-template <typename T, int MODE>
+// FULL: the right transform is 64 wide (compile-time widths keep the benchmarked shape free of the narrow-case tests)
+template <typename T, int MODE, bool FULL>
 __global__ void __launch_bounds__(kThreads, 1)
 flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restrict__ left, const T* __restrict__ right,
-                     void* __restrict__ out, void* __restrict__ scales, long long tokens, int m, float clip,
+                     void* __restrict__ out, void* __restrict__ scales, long long tokens, int m, int nc_arg, float clip,
                      int scale_dtype, uint32_t* __restrict__ status) {
+  const int nc = FULL ? 64 : nc_arg;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Misc* misc = reinterpret_cast<Misc*>(smem + kOffMisc);
@@ -84,6 +88,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
     const int cc = (qq * 32) / mpad;
     nq2 += (cc < kGroup && qq * 32 - cc * mpad < m) ? 1 : 0;
   }
+  const int nh2 = (nc + 31) >> 5;             // 32-column halves of Z that hold real columns
   int mine = 0;                               // groups this CTA works on
   if ((long long)blockIdx.x < ngroups) mine = (int)((ngroups - blockIdx.x + gridDim.x - 1) / gridDim.x);
 
@@ -97,8 +102,8 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&misc->d2_full[i]), 1);
-      mbar_init(smem_u32(&misc->d2_empty[i]), 2 * nq2);  // one arrival per working warp of a quantize set
-      mbar_init(smem_u32(&misc->set_sync[i]), 2 * nq2);
+      mbar_init(smem_u32(&misc->d2_empty[i]), nh2 * nq2);  // one arrival per working warp of a quantize set
+      mbar_init(smem_u32(&misc->set_sync[i]), nh2 * nq2);
     }
     for (int i = 0; i < 2 * 3 * 2 * 4; ++i) (&misc->absmax_part[0][0][0][0])[i] = 0.f;
     fence_barrier_init();
@@ -126,7 +131,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
     uint16_t* raw_l = reinterpret_cast<uint16_t*>(smem + kOffY);
     uint16_t* raw_r = reinterpret_cast<uint16_t*>(smem + kOffY + kStageBytes);
     {
-      const int l_chunks = (m * m) / 8, r_chunks = 64 * 64 / 8;
+      const int l_chunks = (m * m) / 8, r_chunks = nc * nc / 8;
       constexpr int kMaxIter = (2 * 64 * 64 / 8 + kStagers - 1) / kStagers;
       uint4 tmp[kMaxIter];
 #pragma unroll
@@ -147,10 +152,12 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
     // 2-byte reads of a warp are contiguous and each thread makes one 16-byte swizzled store.
     for (int idx = t13; idx < 64 * 8; idx += kStagers) {
       const int n = idx & 63, jc = idx >> 6;
-      uint32_t w[4];
+      uint32_t w[4] = {0, 0, 0, 0};  // rows and columns past N stay zero
+      if (n < nc && 8 * jc < nc) {
 #pragma unroll
-      for (int e2 = 0; e2 < 4; ++e2)
-        w[e2] = (uint32_t)raw_r[(8 * jc + 2 * e2) * 64 + n] | ((uint32_t)raw_r[(8 * jc + 2 * e2 + 1) * 64 + n] << 16);
+        for (int e2 = 0; e2 < 4; ++e2)
+          w[e2] = (uint32_t)raw_r[(8 * jc + 2 * e2) * nc + n] | ((uint32_t)raw_r[(8 * jc + 2 * e2 + 1) * nc + n] << 16);
+      }
       *reinterpret_cast<uint4*>(smem + kOffR + (n >> 3) * 1024 + (n & 7) * 128 + ((jc ^ (n & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
     }
     // LL, K-major: row (copy, i) = copy * mpad + i, column k holds L[k][i]; all other rows and the columns past m are zero
@@ -214,8 +221,13 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
         tc_fence_after();
         TR(1, it, 1);
         const uint64_t da = desc_x0 + (uint64_t)(sx * (kStageBytes >> 4));
+        if (FULL) {  // four back-to-back issues without loop overhead
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) mma_f16_ss(tmem + s1 * 64, da + ks * 2, desc_r + ks * 2, idesc1, ks);
+          for (int ks = 0; ks < 4; ++ks) mma_f16_ss(tmem + s1 * 64, da + ks * 2, desc_r + ks * 2, idesc1, ks);
+        } else {
+#pragma unroll 1
+          for (int ks = 0; ks < (nc >> 4); ++ks) mma_f16_ss(tmem + s1 * 64, da + ks * 2, desc_r + ks * 2, idesc1, ks);
+        }
         mma_commit(smem_u32(&misc->empty_x[sx]));
         mma_commit(smem_u32(&misc->d1_full[s1]));
         TR(1, it, 2);
@@ -291,9 +303,10 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
     const int c = l / mpad, mi = l - c * mpad;      // lane block c holds a copy of the Z rows: it serves token c
     const bool active = c < kGroup && mi < m;
     const int slot = ((q * 32 - c * mpad) >> 5) * 2 + h;  // this warp's index among the (at most 4) warps of its token
-    const int feat = m * 64;
+    const int feat = m * nc;
+    const int cols = FULL ? 32 : min(32, max(0, nc - h * 32));  // real columns among this warp's 32 (a multiple of 16)
     long long grp = (long long)blockIdx.x + (long long)e * gridDim.x;
-    const int mine_q = ((q * 32) / mpad < kGroup && q * 32 - ((q * 32) / mpad) * mpad < m) ? mine : 0;  // idle quadrants skip the pass
+    const int mine_q = ((q * 32) / mpad < kGroup && q * 32 - ((q * 32) / mpad) * mpad < m && cols > 0) ? mine : 0;  // idle warps skip the pass
     for (int use = 0, it = e; it < mine_q; it += 2, ++use, grp += 2LL * gridDim.x) {
       const int ph = use & 1, buf = use % 3;
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&misc->d2_full[e]), ph))) { atomicCAS(status, 0u, 0x800u + e); break; }
@@ -359,10 +372,10 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
         const int c0 = h * 32;
         if (MODE == kTransform) {
           if (valid) {
-            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + tok * feat + mi * 64 + c0);
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + tok * feat + mi * nc + c0);
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-              dst[j] = make_float4(DT<T>::rnd(__uint_as_float(v[4 * j])), DT<T>::rnd(__uint_as_float(v[4 * j + 1])),
+              if (4 * j < cols) dst[j] = make_float4(DT<T>::rnd(__uint_as_float(v[4 * j])), DT<T>::rnd(__uint_as_float(v[4 * j + 1])),
                                    DT<T>::rnd(__uint_as_float(v[4 * j + 2])), DT<T>::rnd(__uint_as_float(v[4 * j + 3])));
           }
         } else if (MODE == kPacked && !zero_scale) {
@@ -374,10 +387,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
 #pragma unroll
             for (int j = 0; j < 4; ++j) w[j] = quantize8<T, false>(&zz[4 * j], s, inv_s, rhi2, rlo2);
           }
-          if (valid) {
-            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(out) + tok * (feat / 8) + (mi * 64 + c0) / 8);
-            *dst = make_uint4(w[0], w[1], w[2], w[3]);
-          }
+          if (valid) store_words(reinterpret_cast<uint32_t*>(out) + tok * (feat / 8) + (mi * nc + c0) / 8, w, cols);
         } else {
           uint32_t pb[4], qb[4];
           if (!zero_scale) {
@@ -399,13 +409,13 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
           }
           if (MODE == kPacked) {
             if (valid) {
-              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint32_t*>(out) + tok * (feat / 8) + (mi * 64 + c0) / 8);
-              *dst = make_uint4(pack8(pb[0], qb[0]), pack8(pb[1], qb[1]), pack8(pb[2], qb[2]), pack8(pb[3], qb[3]));
+              const uint32_t w[4] = {pack8(pb[0], qb[0]), pack8(pb[1], qb[1]), pack8(pb[2], qb[2]), pack8(pb[3], qb[3])};
+              store_words(reinterpret_cast<uint32_t*>(out) + tok * (feat / 8) + (mi * nc + c0) / 8, w, cols);
             }
           } else if (valid) {
-            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<int8_t*>(out) + tok * feat + mi * 64 + c0);
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<int8_t*>(out) + tok * feat + mi * nc + c0);  // 16-byte aligned: N % 16 == 0
             dst[0] = make_uint4(bytes4(pb[0]), bytes4(qb[0]), bytes4(pb[1]), bytes4(qb[1]));
-            dst[1] = make_uint4(bytes4(pb[2]), bytes4(qb[2]), bytes4(pb[3]), bytes4(qb[3]));
+            if (cols > 16) dst[1] = make_uint4(bytes4(pb[2]), bytes4(qb[2]), bytes4(pb[3]), bytes4(qb[3]));
           }
         }
       }
@@ -421,10 +431,10 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
   }
 }
 
-template <typename T, int MODE>
+template <typename T, int MODE, bool FULL>
 int launch_one(const CUtensorMap& map, const void* left, const void* right, void* out, void* scales, int64_t tokens, int m,
-               float clip, int scale_dtype, uint32_t* status, cudaStream_t stream) {
-  auto kern = flatquant_n64_kernel<T, MODE>;
+               int nc, float clip, int scale_dtype, uint32_t* status, cudaStream_t stream) {
+  auto kern = flatquant_n64_kernel<T, MODE, FULL>;
   int dev = 0, sms = 148;
   QO_CUDA_TRY(cudaGetDevice(&dev));
   static bool configured[64] = {};
@@ -446,17 +456,24 @@ int launch_one(const CUtensorMap& map, const void* left, const void* right, void
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   QO_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, map, reinterpret_cast<const T*>(left), reinterpret_cast<const T*>(right), out, scales,
-                                 (long long)tokens, m, clip, scale_dtype, status));
+                                 (long long)tokens, m, nc, clip, scale_dtype, status));
   return check_launch("flatquant_n64_kernel");
 }
 
 template <typename T>
 int launch_mode(int mode, const CUtensorMap& map, const void* left, const void* right, void* out, void* scales,
-                int64_t tokens, int m, float clip, int scale_dtype, uint32_t* status, cudaStream_t stream) {
+                int64_t tokens, int m, int nc, float clip, int scale_dtype, uint32_t* status, cudaStream_t stream) {
+  if (nc == 64) {
+    switch (mode) {
+      case kInt8: return launch_one<T, kInt8, true>(map, left, right, out, scales, tokens, m, nc, clip, scale_dtype, status, stream);
+      case kPacked: return launch_one<T, kPacked, true>(map, left, right, out, scales, tokens, m, nc, clip, scale_dtype, status, stream);
+      default: return launch_one<T, kTransform, true>(map, left, right, out, scales, tokens, m, nc, clip, scale_dtype, status, stream);
+    }
+  }
   switch (mode) {
-    case kInt8: return launch_one<T, kInt8>(map, left, right, out, scales, tokens, m, clip, scale_dtype, status, stream);
-    case kPacked: return launch_one<T, kPacked>(map, left, right, out, scales, tokens, m, clip, scale_dtype, status, stream);
-    default: return launch_one<T, kTransform>(map, left, right, out, scales, tokens, m, clip, scale_dtype, status, stream);
+    case kInt8: return launch_one<T, kInt8, false>(map, left, right, out, scales, tokens, m, nc, clip, scale_dtype, status, stream);
+    case kPacked: return launch_one<T, kPacked, false>(map, left, right, out, scales, tokens, m, nc, clip, scale_dtype, status, stream);
+    default: return launch_one<T, kTransform, false>(map, left, right, out, scales, tokens, m, nc, clip, scale_dtype, status, stream);
   }
 }
 
@@ -468,15 +485,15 @@ extern "C" __attribute__((visibility("default"))) int qo_debug_set_trace(long lo
 }
 #endif
 
-bool flatquant_sm100_n64_supported(int m, int n) { return n == 64 && m >= 16 && m <= 64 && (m % 8) == 0; }
+bool flatquant_sm100_n64_supported(int m, int n) { return n >= 16 && n <= 64 && (n % 16) == 0 && m >= 16 && m <= 64 && (m % 8) == 0; }
 
 int launch_flatquant_sm100_n64(int mode, const void* x_map, const void* left, const void* right, void* out, void* scales,
-                               int64_t tokens, int m, float clip, int in_dtype, int scale_dtype, uint32_t* status,
+                               int64_t tokens, int m, int n, float clip, int in_dtype, int scale_dtype, uint32_t* status,
                                cudaStream_t stream) {
   const CUtensorMap& map = *reinterpret_cast<const CUtensorMap*>(x_map);
   if (in_dtype == QO_BF16)
-    return launch_mode<__nv_bfloat16>(mode, map, left, right, out, scales, tokens, m, clip, scale_dtype, status, stream);
-  return launch_mode<__half>(mode, map, left, right, out, scales, tokens, m, clip, scale_dtype, status, stream);
+    return launch_mode<__nv_bfloat16>(mode, map, left, right, out, scales, tokens, m, n, clip, scale_dtype, status, stream);
+  return launch_mode<__half>(mode, map, left, right, out, scales, tokens, m, n, clip, scale_dtype, status, stream);
 }
 
 }  // namespace qo

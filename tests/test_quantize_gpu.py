@@ -93,7 +93,9 @@ def test_against_oracle(tokens, feat, dtype, clip, pack, outliers):
 
 WIDE = [(16, "bf16", 37, True), (32, "fp16", 9, False), (48, "bf16", 5, True), (64, "bf16", 131, True), (40, "bf16", 6, True),
         (100, "fp16", 3, True), (112, "bf16", 300, True), (128, "bf16", 4, False), (86, "fp16", 150, False)]
-NARROWER = [(64, 80, "bf16", 150, True), (64, 96, "bf16", 33, True), (64, 112, "fp16", 150, False), (100, 96, "bf16", 7, True),
+NARROWER = [(32, 32, "bf16", 149, True), (32, 48, "fp16", 77, True), (16, 16, "bf16", 33, False), (24, 32, "bf16", 5, True),
+            (64, 48, "bf16", 6, False), (48, 16, "fp16", 300, True),
+            (64, 80, "bf16", 150, True), (64, 96, "bf16", 33, True), (64, 112, "fp16", 150, False), (100, 96, "bf16", 7, True),
             (32, 80, "fp16", 9, True), (48, 112, "bf16", 10, False), (128, 80, "bf16", 5, True), (72, 112, "bf16", 149, True)]
 
 
@@ -108,8 +110,9 @@ def test_right_transform_of_size_128(m, dtype, tokens, pack):
 
 
 @pytest.mark.parametrize("m,n,dtype,tokens,pack", NARROWER)
-def test_right_transforms_of_80_96_112(m, n, dtype, tokens, pack):
-    """5120 = 64 x 80, 6144 = 64 x 96, 7168 = 64 x 112 and relatives run in the kernel for N = 128 with zero-padded columns."""
+def test_right_transforms_other_than_64_and_128(m, n, dtype, tokens, pack):
+    """1024 = 32 x 32, 1536 = 32 x 48, 5120 = 64 x 80, 6144 = 64 x 96, 7168 = 64 x 112 and relatives run in the kernels for
+    N = 64 / N = 128 with zero-padded columns."""
     x, left, right = make_inputs(tokens, m * n, dtype, 13 * m + n + tokens, True, mn=(m, n))
     ref_codes, ref_scales = O.flatquant_quantize(t2f(x), t2f(left), t2f(right), 0.9, pack, dtype)
     for label, codes, scales in run_both(x, left, right, 0.9, pack, dtype):
