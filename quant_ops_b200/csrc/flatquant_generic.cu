@@ -2,9 +2,11 @@
 //
 // Covers every (M, N) and all three activation dtypes; the tcgen05 kernel in flatquant_sm100.cu takes over for
 // the 16-bit shapes it supports.  One CTA works on one token at a time (grid-stride over tokens): the token's
-// M x N matrix is staged in shared memory as float, the two small products are evaluated with float32 FMA in
-// ascending-k order and rounded to the activation dtype where the reference rounds, then the row extremes give
-// the scale and the codes are written 8 at a time.
+// M x N matrix is staged in shared memory in the activation dtype (every value kept there is a value of that dtype:
+// X as given, Y and Z after their rounding), the two small products are evaluated with float32 FMA in ascending-k
+// order and rounded to the activation dtype where the reference rounds, then the row extremes give the scale and the
+// codes are written 8 at a time.  Two buffers of M*N elements: 16-bit inputs up to 51,200 features (28672 = 128 x 224
+// and 32768 = 128 x 256 included), float32 inputs up to 25,600.
 //
 // Numerics follow flatquant_pytorch (reference: src/quant_ops/ops/quantization/flatquant/ops.py:99-117).
 #include "qo_internal.cuh"
@@ -21,10 +23,10 @@ __global__ void __launch_bounds__(kThreads)
 flatquant_generic_kernel(const T* __restrict__ x, int64_t ldx, const T* __restrict__ left,
                          const T* __restrict__ right, void* __restrict__ codes, void* __restrict__ scales,
                          int64_t tokens, int m, int n, float clip, int scale_dtype) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) unsigned char smem_bytes[];
   const int feat = m * n;
-  float* bufx = smem;         // X, later Z
-  float* bufy = smem + feat;  // Y = round(X . R)
+  T* bufx = reinterpret_cast<T*>(smem_bytes);  // X, later Z
+  T* bufy = bufx + feat;                       // Y = round(X . R)
   __shared__ float red_min[kThreads / 32], red_max[kThreads / 32];
   __shared__ float s_scale;
 
@@ -34,7 +36,7 @@ flatquant_generic_kernel(const T* __restrict__ x, int64_t ldx, const T* __restri
 
   for (int64_t tok = blockIdx.x; tok < tokens; tok += gridDim.x) {
     const T* xr = x + tok * ldx;
-    for (int i = tid; i < feat; i += kThreads) bufx[i] = DT<T>::load(xr + i);
+    for (int i = tid; i < feat; i += kThreads) bufx[i] = xr[i];
     __syncthreads();
 
     // Y[r][c] = sum_j X[r][j] * R[j][c]
@@ -48,12 +50,12 @@ flatquant_generic_kernel(const T* __restrict__ x, int64_t ldx, const T* __restri
 #pragma unroll
         for (int i = 0; i < kRowsPerItem; ++i) {
           const int r = min(r0 + i, m - 1);
-          acc[i] = fmaf(bufx[r * n + j], rv, acc[i]);
+          acc[i] = fmaf(DT<T>::load(bufx + r * n + j), rv, acc[i]);
         }
       }
 #pragma unroll
       for (int i = 0; i < kRowsPerItem; ++i)
-        if (r0 + i < m) bufy[(r0 + i) * n + c] = DT<T>::rnd(acc[i]);
+        if (r0 + i < m) DT<T>::store(bufy + (r0 + i) * n + c, acc[i]);
     }
     __syncthreads();
 
@@ -65,7 +67,7 @@ flatquant_generic_kernel(const T* __restrict__ x, int64_t ldx, const T* __restri
 #pragma unroll
       for (int i = 0; i < kRowsPerItem; ++i) acc[i] = 0.f;
       for (int k = 0; k < m; ++k) {
-        const float yv = bufy[k * n + c];
+        const float yv = DT<T>::load(bufy + k * n + c);
 #pragma unroll
         for (int i = 0; i < kRowsPerItem; ++i) {
           const int r = min(r0 + i, m - 1);
@@ -76,7 +78,7 @@ flatquant_generic_kernel(const T* __restrict__ x, int64_t ldx, const T* __restri
       for (int i = 0; i < kRowsPerItem; ++i) {
         if (r0 + i < m) {
           const float z = DT<T>::rnd(acc[i]);
-          bufx[(r0 + i) * n + c] = z;
+          DT<T>::store(bufx + (r0 + i) * n + c, z);
           lmin = fminf(lmin, z);
           lmax = fmaxf(lmax, z);
         }
@@ -85,7 +87,7 @@ flatquant_generic_kernel(const T* __restrict__ x, int64_t ldx, const T* __restri
     if (MODE == 2) {
       __syncthreads();
       float* zout = reinterpret_cast<float*>(codes) + tok * (int64_t)feat;
-      for (int i = tid; i < feat; i += kThreads) zout[i] = bufx[i];
+      for (int i = tid; i < feat; i += kThreads) zout[i] = DT<T>::load(bufx + i);
       __syncthreads();
       continue;
     }
@@ -117,12 +119,12 @@ flatquant_generic_kernel(const T* __restrict__ x, int64_t ldx, const T* __restri
       for (int p = tid; p < feat / 8; p += kThreads) {
         uint32_t w = 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) w |= (uint32_t)(quantize_one<T>(bufx[p * 8 + i], s) + 8) << (4 * i);
+        for (int i = 0; i < 8; ++i) w |= (uint32_t)(quantize_one<T>(DT<T>::load(bufx + p * 8 + i), s) + 8) << (4 * i);
         out[p] = (int32_t)w;
       }
     } else {
       int8_t* out = reinterpret_cast<int8_t*>(codes) + tok * (int64_t)feat;
-      for (int i = tid; i < feat; i += kThreads) out[i] = (int8_t)quantize_one<T>(bufx[i], s);
+      for (int i = tid; i < feat; i += kThreads) out[i] = (int8_t)quantize_one<T>(DT<T>::load(bufx + i), s);
     }
     __syncthreads();  // bufx is refilled by the next token
   }
@@ -131,7 +133,7 @@ flatquant_generic_kernel(const T* __restrict__ x, int64_t ldx, const T* __restri
 template <typename T>
 int launch_typed(const void* x, int64_t ldx, const void* left, const void* right, void* codes, void* scales,
                  int64_t tokens, int m, int n, float clip, int pack, int scale_dtype, cudaStream_t stream) {
-  const size_t smem = (size_t)2 * m * n * sizeof(float);
+  const size_t smem = (size_t)2 * m * n * sizeof(T);
   if (smem > 200 * 1024) return fail(QO_ERR_UNSUPPORTED, "flatquant: m*n = %d is too large for the generic kernel", m * n);
   int dev = 0, sms = 148;
   QO_CUDA_TRY(cudaGetDevice(&dev));

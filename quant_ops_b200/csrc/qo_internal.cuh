@@ -70,6 +70,7 @@ template <>
 struct DT<float> {
   static constexpr int id = QO_F32;
   __device__ __forceinline__ static float load(const float* p) { return *p; }
+  __device__ __forceinline__ static void store(float* p, float v) { *p = v; }
   __device__ __forceinline__ static float rnd(float v) { return v; }
   __device__ __forceinline__ static float floor_scale() { return 1e-8f; }
 };
@@ -77,6 +78,7 @@ template <>
 struct DT<__half> {
   static constexpr int id = QO_F16;
   __device__ __forceinline__ static float load(const __half* p) { return __half2float(*p); }
+  __device__ __forceinline__ static void store(__half* p, float v) { *p = __float2half_rn(v); }
   __device__ __forceinline__ static float rnd(float v) { return __half2float(__float2half_rn(v)); }
   __device__ __forceinline__ static float floor_scale() { return 0.f; }  // 1e-8 rounds to 0 in fp16
 };
@@ -84,6 +86,7 @@ template <>
 struct DT<__nv_bfloat16> {
   static constexpr int id = QO_BF16;
   __device__ __forceinline__ static float load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+  __device__ __forceinline__ static void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
   __device__ __forceinline__ static float rnd(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
   __device__ __forceinline__ static float floor_scale() { return __bfloat162float(__float2bfloat16_rn(1e-8f)); }
 };

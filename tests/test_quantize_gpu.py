@@ -136,6 +136,17 @@ def test_right_transform_of_size_64_small_left(m, dtype, tokens, pack):
         check(codes, scales, ref_codes, ref_scales, pack)
 
 
+@pytest.mark.parametrize("feat,dtype", [(28672, "bf16"), (32768, "fp16"), (24576, "fp32")])
+def test_very_wide_rows_take_the_generic_kernel(feat, dtype):
+    """28672 = 128 x 224 (the down-projection input of the 70B-class models) and 32768 = 128 x 256 have no tensor-core
+    kernel (right transform above 128); the SIMT kernel must take them."""
+    x, left, right = make_inputs(3, feat, dtype, feat + 3, True)
+    ref_codes, ref_scales = O.flatquant_quantize(t2f(x), t2f(left), t2f(right), 0.9, True, dtype)
+    codes, scales = abi_quantize(x.to(DEV), left.to(DEV), right.to(DEV), 0.9, True, dtype, policy=0)
+    assert lib.qo_last_quantizer_path() == 1
+    check(codes.cpu().numpy(), t2f(scales), ref_codes, ref_scales, True)
+
+
 def test_activation_scale_config_sampled_rows():
     """8192 x 4096 bf16, 1 % outlier channels, clip 0.9, packed: every row quantized on the GPU, a seeded sample of
     rows compared with the oracle (rows are independent), and a dequantize round trip over everything."""
