@@ -8,27 +8,39 @@ namespace {
 constexpr int kThreads = 256;
 
 // ---- dequantize: reference src/quant_ops/ops/quantization/flatquant/ops.py:156-178 ----------------
-// packed: one thread per int32 word -> 8 floats (two 16-byte stores)
+// packed: one thread per half word -> 4 floats, so that consecutive lanes write consecutive 16-byte pieces (a warp's
+// store covers 512 contiguous bytes); four items per thread are in flight.  The output is 8x the input: the kernel is
+// bound by HBM writes.
 __global__ void __launch_bounds__(kThreads)
 dequant_packed_kernel(const uint32_t* __restrict__ words, const void* __restrict__ scales, float* __restrict__ out,
                       int64_t tokens, int64_t words_per_row, int scale_dtype) {
-  const int64_t total = tokens * words_per_row;
-  for (int64_t i = blockIdx.x * (int64_t)kThreads + threadIdx.x; i < total; i += (int64_t)gridDim.x * kThreads) {
-    const int64_t t = i / words_per_row;
-    const float s = load_scale(scales, t, scale_dtype);
-    const uint32_t w = words[i];
-    float4 lo, hi;
-    lo.x = (float)((int)(w & 0xF) - 8) * s;
-    lo.y = (float)((int)((w >> 4) & 0xF) - 8) * s;
-    lo.z = (float)((int)((w >> 8) & 0xF) - 8) * s;
-    lo.w = (float)((int)((w >> 12) & 0xF) - 8) * s;
-    hi.x = (float)((int)((w >> 16) & 0xF) - 8) * s;
-    hi.y = (float)((int)((w >> 20) & 0xF) - 8) * s;
-    hi.z = (float)((int)((w >> 24) & 0xF) - 8) * s;
-    hi.w = (float)((int)((w >> 28) & 0xF) - 8) * s;
-    float4* o = reinterpret_cast<float4*>(out + i * 8);
-    o[0] = lo;
-    o[1] = hi;
+  constexpr int kUnroll = 4;
+  const int64_t total = tokens * words_per_row * 2;  // 16-byte output pieces
+  const int64_t stride = (int64_t)gridDim.x * kThreads;
+  for (int64_t i0 = blockIdx.x * (int64_t)kThreads + threadIdx.x; i0 < total; i0 += stride * kUnroll) {
+    uint32_t w[kUnroll];
+    float s[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < total) {
+        const int64_t word = i >> 1;
+        w[u] = words[word] >> (16 * (int)(i & 1));  // the four nibbles of this half
+        s[u] = load_scale(scales, word / words_per_row, scale_dtype);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < total) {
+        float4 o;
+        o.x = (float)((int)(w[u] & 0xF) - 8) * s[u];
+        o.y = (float)((int)((w[u] >> 4) & 0xF) - 8) * s[u];
+        o.z = (float)((int)((w[u] >> 8) & 0xF) - 8) * s[u];
+        o.w = (float)((int)((w[u] >> 12) & 0xF) - 8) * s[u];
+        __stcs(reinterpret_cast<float4*>(out) + i, o);  // streaming store: the output is not read back by this kernel
+      }
+    }
   }
 }
 
@@ -38,12 +50,25 @@ dequant_int8_kernel(const int8_t* __restrict__ codes, const void* __restrict__ s
                     int64_t tokens, int64_t features, int scale_dtype) {
   const int64_t total = tokens * features;
   if ((features & 3) == 0) {
-    const int64_t groups = total >> 2;
-    for (int64_t g = blockIdx.x * (int64_t)kThreads + threadIdx.x; g < groups; g += (int64_t)gridDim.x * kThreads) {
-      const int64_t t = (g << 2) / features;
-      const float s = load_scale(scales, t, scale_dtype);
-      const char4 c = reinterpret_cast<const char4*>(codes)[g];
-      reinterpret_cast<float4*>(out)[g] = make_float4((float)c.x * s, (float)c.y * s, (float)c.z * s, (float)c.w * s);
+    constexpr int kUnroll = 4;
+    const int64_t groups = total >> 2, stride = (int64_t)gridDim.x * kThreads;
+    for (int64_t g0 = blockIdx.x * (int64_t)kThreads + threadIdx.x; g0 < groups; g0 += stride * kUnroll) {
+      char4 c[kUnroll];
+      float s[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int64_t g = g0 + u * stride;
+        if (g < groups) {
+          c[u] = reinterpret_cast<const char4*>(codes)[g];
+          s[u] = load_scale(scales, (g << 2) / features, scale_dtype);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int64_t g = g0 + u * stride;
+        if (g < groups)
+          __stcs(reinterpret_cast<float4*>(out) + g, make_float4((float)c[u].x * s[u], (float)c[u].y * s[u], (float)c[u].z * s[u], (float)c[u].w * s[u]));
+      }
     }
   } else {
     for (int64_t i = blockIdx.x * (int64_t)kThreads + threadIdx.x; i < total; i += (int64_t)gridDim.x * kThreads)
@@ -120,11 +145,11 @@ int launch_dequantize(const void* codes, const void* scales, float* out, int64_t
                       int scale_dtype, cudaStream_t stream) {
   if (packed) {
     const int64_t wpr = features / 8;
-    dequant_packed_kernel<<<grid_for(tokens * wpr), kThreads, 0, stream>>>(
+    dequant_packed_kernel<<<grid_for((tokens * wpr * 2 + 3) / 4), kThreads, 0, stream>>>(
         reinterpret_cast<const uint32_t*>(codes), scales, out, tokens, wpr, scale_dtype);
     return check_launch("dequant_packed_kernel");
   }
-  dequant_int8_kernel<<<grid_for(tokens * features / 4 + 1), kThreads, 0, stream>>>(
+  dequant_int8_kernel<<<grid_for(tokens * features / 16 + 1), kThreads, 0, stream>>>(
       reinterpret_cast<const int8_t*>(codes), scales, out, tokens, features, scale_dtype);
   return check_launch("dequant_int8_kernel");
 }
