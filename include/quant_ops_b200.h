@@ -143,7 +143,8 @@ QO_API int qo_int4_matmul(const int32_t* a, int64_t lda, const int32_t* b, int64
  * library holds qo_int4_matmul_static_max_bytes() (8 MiB) until the process exits.
  *
  * Limits and rules:
- *   - tokens*k + n_out*k bytes (each rounded up to 256) must not exceed qo_int4_matmul_static_max_bytes(); larger
+ *   - tokens*k bytes (rounded up to 256) + ceil(n_out/256)*256 * ceil(k/128)*128 bytes (the weights are held in
+ *     whole blocks of 256 channels x 128 values) must not exceed qo_int4_matmul_static_max_bytes(); larger
  *     problems return QO_ERR_WORKSPACE.  Only the shapes of the tcgen05 kernel are served (k % 16 == 0,
  *     n_out % 8 == 0, b with unit stride along k or along n_out); others return QO_ERR_UNSUPPORTED.
  *   - the first call on a device looks up the array's device address; make it before any stream capture.

@@ -290,19 +290,18 @@ int qo_w4a4_linear(const void* x, int64_t ldx, const void* left, const void* rig
   char* ws = reinterpret_cast<char*>(workspace);
   if (t_policy != 1 && tokens > 32 && gemm_sm100_supported(tokens, k, n_out, k / 8, 1, k / 8)) {
     // tensor-core route: the quantizer writes int8 codes, which is the GEMM's A operand as it is; only the weights
-    // are widened.  Layout: int8 codes [tokens, k] | scales | int8 weights [n_out, k] | K-split partial sums.
+    // are widened.  Layout: int8 codes [tokens, k] | scales | int8 weights (blocked).
     int8_t* a8 = reinterpret_cast<int8_t*>(ws);
     const size_t o_scale = align_up((size_t)tokens * (size_t)k, 256);
     float* a_scale8 = reinterpret_cast<float*>(ws + o_scale);
     const size_t o_b = o_scale + align_up((size_t)tokens * 4, 256);
     int8_t* b8 = reinterpret_cast<int8_t*>(ws + o_b);
-    int32_t* part = gemm_k_split(tokens, k, n_out) > 1 ? reinterpret_cast<int32_t*>(ws + o_b + align_up((size_t)n_out * (size_t)k, 256)) : nullptr;
     rc = qo_flatquant_quantize(x, ldx, left, right, a8, a_scale8, tokens, m, n, clip_ratio, in_dtype, 0, QO_F32, stream);
     if (rc) return rc;
-    if ((rc = launch_widen_rows(w_packed, k / 8, b8, n_out, k, reinterpret_cast<cudaStream_t>(stream)))) return rc;
+    if ((rc = launch_widen_rows(w_packed, k / 8, b8, n_out, k, reinterpret_cast<cudaStream_t>(stream), true))) return rc;
     t_gemm_path = 2;
     return launch_gemm_sm100_s8(a8, b8, a_scale8, w_scale, out, out_dtype, tokens, k, n_out, nullptr, bias,
-                                reinterpret_cast<cudaStream_t>(stream), part);
+                                reinterpret_cast<cudaStream_t>(stream));
   }
   int32_t* a_packed = reinterpret_cast<int32_t*>(ws);
   const size_t off_scale = align_up((size_t)tokens * (size_t)(k / 8) * 4, 256);
@@ -320,7 +319,7 @@ int qo_w4a4_linear(const void* x, int64_t ldx, const void* left, const void* rig
 
 size_t qo_prepared_weights_bytes(int64_t n_out, int64_t k) {
   if (n_out <= 0 || k <= 0) return 0;
-  return align_up((size_t)n_out * (size_t)k, 256);
+  return gemm_b8_bytes(n_out, k);
 }
 
 int qo_prepare_weights(const int32_t* w_packed, void* prepared, int64_t n_out, int64_t k, void* stream) {
@@ -331,14 +330,13 @@ int qo_prepare_weights(const int32_t* w_packed, void* prepared, int64_t n_out, i
   if (reinterpret_cast<uintptr_t>(prepared) % 256) return fail(QO_ERR_INVALID_ARGUMENT, "prepare_weights: the prepared buffer must be 256-byte aligned");
   int rc = require_device(nullptr);
   if (rc) return rc;
-  return launch_widen_rows(w_packed, k / 8, reinterpret_cast<int8_t*>(prepared), n_out, k, reinterpret_cast<cudaStream_t>(stream));
+  return launch_widen_rows(w_packed, k / 8, reinterpret_cast<int8_t*>(prepared), n_out, k, reinterpret_cast<cudaStream_t>(stream), true);
 }
 
-// layout of the prepared layer's workspace: int8 codes [tokens, k] | float scales [tokens] | K-split partial sums
+// layout of the prepared layer's workspace: int8 codes [tokens, k] | float scales [tokens]
 size_t qo_w4a4_linear_prepared_workspace_bytes(int64_t tokens, int64_t k, int64_t n_out) {
   if (tokens <= 0 || k <= 0) return 0;
-  const size_t direct = align_up((size_t)tokens * (size_t)k, 256) + align_up((size_t)tokens * 4, 256) +
-                        (gemm_k_split(tokens, k, n_out) > 1 ? align_up((size_t)tokens * (size_t)n_out * 4, 256) : 0);
+  const size_t direct = align_up((size_t)tokens * (size_t)k, 256) + align_up((size_t)tokens * 4, 256);
   const size_t packed = qo_w4a4_linear_workspace_bytes(tokens, k, n_out);  // shapes that take the packed-weight route
   return direct > packed ? direct : packed;
 }
@@ -372,12 +370,11 @@ int qo_w4a4_linear_prepared(const void* x, int64_t ldx, const void* left, const 
   int8_t* a8 = reinterpret_cast<int8_t*>(ws);
   const size_t off_scale = align_up((size_t)tokens * (size_t)k, 256);
   float* a_scale = reinterpret_cast<float*>(ws + off_scale);
-  int32_t* part = gemm_k_split(tokens, k, n_out) > 1 ? reinterpret_cast<int32_t*>(ws + off_scale + align_up((size_t)tokens * 4, 256)) : nullptr;
   rc = qo_flatquant_quantize(x, ldx, left, right, a8, a_scale, tokens, m, n, clip_ratio, in_dtype, 0, QO_F32, stream);
   if (rc) return rc;
   t_gemm_path = 2;
   return launch_gemm_sm100_s8(a8, reinterpret_cast<const int8_t*>(prepared), a_scale, w_scale, out, out_dtype, tokens, k, n_out,
-                              nullptr, bias, reinterpret_cast<cudaStream_t>(stream), part);
+                              nullptr, bias, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int qo_pack_int4(const int8_t* codes, int32_t* packed, int64_t rows, int64_t features, void* stream) {

@@ -1,9 +1,12 @@
 // Packed-int4 GEMM for sm_100a.
 //
 // Two steps on the caller's stream:
-//   1. widen: each packed operand is rewritten once as signed bytes, K contiguous (A8 [T, K], B8 [Nout, K]), into
-//      the workspace.  Doing this in a pass of its own keeps the GEMM main loop free of ALU work and of extra
-//      shared-memory traffic; the bytes written stay in the 126 MB L2 for the GEMM that follows.
+//   1. widen: each packed operand is rewritten once as signed bytes into the workspace: A8 [T, K] row-major, B8 in
+//      blocks of 256 output channels x 128 K-bytes (32 KB each, ordered [Nout / 256][K / 128]), so that every B
+//      slice the GEMM fetches is one contiguous piece of memory instead of 256 pieces of 128 bytes, K bytes apart
+//      (short activation matrices stream the weights from HBM exactly once).  Doing this in a pass of its own keeps
+//      the GEMM main loop free of ALU work and of extra shared-memory traffic; the bytes written stay in the 126 MB
+//      L2 for the GEMM that follows.
 //   2. GEMM: persistent CTAs, one 128 x BN output tile at a time.  Warp 0 streams 128-byte-wide K slices of A8 and
 //      B8 with TMA (128-byte swizzle) through a ring of shared-memory stages, warp 1 issues tcgen05.mma kind::i8
 //      (int8 x int8 -> int32) into tensor memory, warps 2-5 read the accumulators back, apply
@@ -34,13 +37,21 @@ __device__ __forceinline__ uint2 widen8(uint32_t w) {
   return make_uint2(((l | 0x80808080u) - 0x08080808u) ^ 0x80808080u, ((h | 0x80808080u) - 0x08080808u) ^ 0x80808080u);
 }
 
-// rows of packed words with unit stride along K: out[r][8*kw .. 8*kw+7]
+// Byte offset of element (row, kbyte) of a widened operand.  ksteps == 0: row-major with row length k (the A operand);
+// otherwise the blocked layout of the B operand, ksteps = ceil(K / 128) blocks per 256 rows.
+__device__ __forceinline__ int64_t widened_offset(int64_t row, int64_t kbyte, int64_t k, int64_t ksteps) {
+  if (ksteps == 0) return row * k + kbyte;
+  return (((row >> 8) * ksteps + (kbyte >> 7)) << 15) + ((row & 255) << 7) + (kbyte & 127);
+}
+
+// rows of packed words with unit stride along K, 8 bytes out per thread
 __global__ void __launch_bounds__(256)
-widen_rows_kernel(const uint32_t* __restrict__ in, int64_t ld_words, uint2* __restrict__ out, int64_t rows, int64_t kwords) {
+widen_rows_kernel(const uint32_t* __restrict__ in, int64_t ld_words, uint8_t* __restrict__ out, int64_t rows, int64_t kwords,
+                  int64_t ksteps) {
   const int64_t total = rows * kwords;
   for (int64_t i = blockIdx.x * 256LL + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
     const int64_t r = i / kwords, kw = i - r * kwords;
-    out[i] = widen8(in[r * ld_words + kw]);
+    *reinterpret_cast<uint2*>(out + widened_offset(r, 8 * kw, 8 * kwords, ksteps)) = widen8(in[r * ld_words + kw]);
   }
 }
 
@@ -48,8 +59,9 @@ widen_rows_kernel(const uint32_t* __restrict__ in, int64_t ld_words, uint2* __re
 // K a multiple of 32): both operands of a GEMM are widened by one kernel.
 struct WidenJob {
   const uint32_t* in;
-  uint4* out;
+  uint8_t* out;
   int64_t ld_words, rows, kquads;  // kquads = K / 32 = groups of four packed words per row
+  int64_t ksteps;                  // 0: row-major output, else the blocked layout
 };
 __global__ void __launch_bounds__(256)
 widen_rows2_kernel(WidenJob j0, WidenJob j1) {
@@ -61,16 +73,17 @@ widen_rows2_kernel(WidenJob j0, WidenJob j1) {
     const int64_t r = e / j.kquads, q = e - r * j.kquads;
     const uint4 w = *reinterpret_cast<const uint4*>(j.in + r * j.ld_words + q * 4);
     const uint2 a = widen8(w.x), b = widen8(w.y), c = widen8(w.z), d = widen8(w.w);
-    j.out[2 * e] = make_uint4(a.x, a.y, b.x, b.y);
-    j.out[2 * e + 1] = make_uint4(c.x, c.y, d.x, d.y);
+    uint4* o = reinterpret_cast<uint4*>(j.out + widened_offset(r, 32 * q, 32 * j.kquads, j.ksteps));
+    o[0] = make_uint4(a.x, a.y, b.x, b.y);
+    o[1] = make_uint4(c.x, c.y, d.x, d.y);
   }
 }
 
-// reference B layout [K/8, N] with N contiguous: transpose 32 x 32 words through shared memory so that both the
-// reads (along N) and the writes (along K) are contiguous
+// reference B layout [K/8, N] with N contiguous: transpose 32 x 32 words through shared memory so that the reads run
+// along N and the writes along K; the output is the blocked layout
 __global__ void __launch_bounds__(256)
-widen_transpose_kernel(const uint32_t* __restrict__ in, int64_t bsk, int64_t bsn, uint2* __restrict__ out, int64_t n,
-                       int64_t kwords) {
+widen_transpose_kernel(const uint32_t* __restrict__ in, int64_t bsk, int64_t bsn, uint8_t* __restrict__ out, int64_t n,
+                       int64_t kwords, int64_t ksteps) {
   __shared__ uint2 tile[32][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
   const int64_t n0 = (int64_t)blockIdx.x * 32, k0 = (int64_t)blockIdx.y * 32;
@@ -85,18 +98,20 @@ widen_transpose_kernel(const uint32_t* __restrict__ in, int64_t bsk, int64_t bsn
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int64_t col = n0 + ty + 8 * i, kw = k0 + tx;
-    if (col < n && kw < kwords) out[col * kwords + kw] = tile[tx][ty + 8 * i];
+    if (col < n && kw < kwords) *reinterpret_cast<uint2*>(out + widened_offset(col, 8 * kw, 8 * kwords, ksteps)) = tile[tx][ty + 8 * i];
   }
 }
 
 // ---- step 2: GEMM --------------------------------------------------------------------------------------------
+// The blocked B operand seen as a matrix of 128-byte rows: first row of the slice (channels n0 .., K step ks)
+__device__ __forceinline__ int b_block_row(int n0, int ks, int ksteps) { return ((n0 >> 8) * ksteps + ks) * 256 + (n0 & 255); }
+
 template <int BN>
 struct GemmCfg {
   static constexpr int kStageBytes = (kBM + BN) * kBK;
   static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int kOffSb = kStages * kStageBytes;           // 4 warps x BN floats
-  static constexpr int kOffTr = kOffSb + 4 * BN * 4;             // 4 warps x 32 x 33 ints: transpose buffer of the K-split epilogue
-  static constexpr int kOffBar = kOffTr + 4 * 32 * 33 * 4;
+  static constexpr int kOffBar = kOffSb + 4 * BN * 4;
   static constexpr int kSmemBytes = kOffBar + 256 + 1024;
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
 };
@@ -130,7 +145,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
                      const float* __restrict__ sa, const float* __restrict__ sb, OutT* __restrict__ out,
                      int32_t* __restrict__ acc_out, const OutT* __restrict__ bias, int t, int n, int k, int ksplit,
-                     int32_t* __restrict__ part, uint32_t* __restrict__ status) {
+                     uint32_t* __restrict__ status) {
   using C = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -138,8 +153,9 @@ gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_con
   const uint32_t smem_base = smem_u32(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tiles_n = (n + BN - 1) / BN, tiles_m = (t + kBM - 1) / kBM;
-  // A work item is an output tile and one of `ksplit` slices of K.  With ksplit > 1 the items add their int32
-  // partial sums into `part` (integer atomics: exact and order-independent) and a second kernel applies the scales.
+  // A work item is an output tile and one of `ksplit` slices of K.  With ksplit > 1 the kernel is launched as
+  // clusters of ksplit CTAs with one work item each (cluster rank = K slice): every CTA of the cluster collects the
+  // slices' int32 partial sums of 128 / ksplit rows of the tile in its shared memory, sums them and writes the outputs.
   const int ntiles = tiles_m * tiles_n * ksplit, ksteps = (k + kBK - 1) / kBK;
 
   if (tid == 0) {
@@ -157,6 +173,9 @@ gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
+  // Launched with programmatic stream serialization: the set-up above may overlap the tail of the preceding kernel
+  // of the stream (the quantizer or the widening pass); nothing below reads or writes global memory before it is done.
+  grid_dependency_wait();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -173,7 +192,7 @@ gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_con
           mbar_arrive_expect_tx(bar, C::kStageBytes);
           const uint32_t dst = smem_base + s * C::kStageBytes;
           tma_load_2d(dst, &a_map, bar, ks * kBK, mb * kBM);
-          tma_load_2d(dst + kBM * kBK, &b_map, bar, ks * kBK, nb * BN);
+          tma_load_2d(dst + kBM * kBK, &b_map, bar, 0, b_block_row(nb * BN, ks, ksteps));
         }
       }
     }
@@ -220,54 +239,45 @@ gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_con
       __syncwarp();
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->acc_full[as]), aph))) { atomicCAS(status, 0u, 0x530u + as); break; }
       tc_fence_after();
-#pragma unroll 2
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + as * BN + c0, v);
-        tmem_ld_wait();
+      // scales, optional bias, 16-byte stores of one row's 32 columns (and the raw accumulators when asked for)
+      auto emit = [&](const uint32_t (&v)[32], int c0) {
         const int col0 = nb * BN + c0;
-        if (part != nullptr) {
-          // K-split: add this slice's partial sums.  A lane holds one row; going through shared memory turns the
-          // 32 x 32 block so that each atomic instruction of the warp covers 32 consecutive columns of one row.
-          int* tr = reinterpret_cast<int*>(smem + C::kOffTr) + (warp - 2) * (32 * 33);
-          __syncwarp();
+        if (!(row_ok && col0 < n)) return;
+        uint32_t w[16];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) tr[lane * 33 + j] = (int)v[j];
-          __syncwarp();
-          const int row0 = mb * kBM + q * 32;
-          if (col0 + lane < n) {
-#pragma unroll 4
-            for (int r = 0; r < 32; ++r)
-              if (row0 + r < t) atomicAdd(part + (int64_t)(row0 + r) * n + col0 + lane, tr[r * 33 + lane]);
-          }
-        } else if (row_ok && col0 < n) {
-          uint32_t w[16];
+        for (int j = 0; j < 16; ++j) {
+          const float f0 = ((float)(int)v[2 * j] * s_row) * sb_s[c0 + 2 * j];
+          const float f1 = ((float)(int)v[2 * j + 1] * s_row) * sb_s[c0 + 2 * j + 1];
+          w[j] = pack_out2<OutT>(f0, f1);
+        }
+        OutT* orow = out + (int64_t)row * n + col0;
+        if (bias != nullptr) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const float f0 = ((float)(int)v[2 * j] * s_row) * sb_s[c0 + 2 * j];
-            const float f1 = ((float)(int)v[2 * j + 1] * s_row) * sb_s[c0 + 2 * j + 1];
-            w[j] = pack_out2<OutT>(f0, f1);
-          }
-          OutT* orow = out + (int64_t)row * n + col0;
-          if (bias != nullptr) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              if (col0 + 2 * j < n) {
-                const float2 o = unpack_out2(w[j], OutT());
-                const float2 b = unpack_out2(*reinterpret_cast<const uint32_t*>(bias + col0 + 2 * j), OutT());
-                w[j] = pack_out2<OutT>(o.x + b.x, o.y + b.y);
-              }
+            if (col0 + 2 * j < n) {
+              const float2 o = unpack_out2(w[j], OutT());
+              const float2 b = unpack_out2(*reinterpret_cast<const uint32_t*>(bias + col0 + 2 * j), OutT());
+              w[j] = pack_out2<OutT>(o.x + b.x, o.y + b.y);
             }
           }
+        }
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            if (col0 + 8 * j < n) reinterpret_cast<uint4*>(orow)[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
-          if (acc_out != nullptr) {
-            int32_t* arow = acc_out + (int64_t)row * n + col0;
+        for (int j = 0; j < 4; ++j)
+          if (col0 + 8 * j < n) reinterpret_cast<uint4*>(orow)[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+        if (acc_out != nullptr) {
+          int32_t* arow = acc_out + (int64_t)row * n + col0;
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (col0 + 4 * j < n) reinterpret_cast<uint4*>(arow)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-          }
+          for (int j = 0; j < 8; ++j)
+            if (col0 + 4 * j < n) reinterpret_cast<uint4*>(arow)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        }
+      };
+      if (ksplit == 1) {
+#pragma unroll 2
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + as * BN + c0, v);
+          tmem_ld_wait();
+          emit(v, c0);
         }
       }
       tc_fence_before();
@@ -275,6 +285,93 @@ gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_con
     }
   }
 
+  if (ksplit > 1) {
+    // K-split (one work item per CTA, accumulator stage 0).  CTA `owner` of the cluster sums and writes rows
+    // [owner * 128 / ksplit, ...) of the tile: every slice sends its int32 partial sums of those rows into slab
+    // [slice] of the owner's shared memory, which reuses the operand stages.  Hence the first barrier: the epilogue
+    // warps come here after their accumulator barrier, so past it every CTA's last MMA has read its operands.
+    // Stores to a peer's shared memory do not wait for a round trip; the second barrier makes them visible, and
+    // after it nobody touches another CTA's memory, so CTAs may leave independently.  Every thread of the cluster
+    // passes both barriers (threads whose wait ran out included: the status word tells).  16-byte pieces are
+    // XOR-swizzled by the row so that neither the stores (a lane per row) nor the reads (a warp per row) meet bank
+    // conflicts.
+    __syncwarp();
+    cluster_sync_all();
+    if (warp >= 2) {
+      // A lane holds one row of the accumulator, but a store to a peer should cover whole 128-byte lines: each
+      // 32-column block is turned through a 4 KB staging area of the warp (behind the slabs), after which 8 lanes
+      // send the 8 pieces of one line.  Staging and slabs use the same swizzle, so pieces are copied in place.
+      const int q = warp & 3, rows_cta = kBM / ksplit;
+      const uint32_t rank = cluster_cta_rank();
+      uint4* stage = reinterpret_cast<uint4*>(smem + kBM * BN * 4) + (warp - 2) * 256;  // 32 rows x 8 pieces
+      const int piece = lane & 7, sub = lane >> 3;
+      tc_fence_after();
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) stage[lane * 8 + (j ^ (lane & 7))] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = q * 32 + i * 4 + sub;
+          const uint32_t owner = (uint32_t)(r / rows_cta), rl = (uint32_t)(r % rows_cta);
+          const uint4 u = stage[(i * 4 + sub) * 8 + piece];
+          const uint32_t slab_piece = smem_base + (((rank * rows_cta + rl) * (BN / 4)) + (uint32_t)((c0 >> 2) + piece)) * 16u;
+          st_cluster_shared_v4(cluster_map_shared(slab_piece, owner), u.x, u.y, u.z, u.w);
+        }
+        __syncwarp();
+      }
+      tc_fence_before();
+    }
+    __syncwarp();
+    cluster_sync_all();
+    if (warp >= 2) {
+      const int rank = (int)cluster_cta_rank(), tile = blockIdx.x / ksplit;
+      const int mb = tile / tiles_n, nb = tile - mb * tiles_n;
+      const int rows_cta = kBM / ksplit;
+      const float* sb_s = reinterpret_cast<float*>(smem + C::kOffSb) + (warp - 2) * BN;  // this warp's copy, filled above
+      const int col = nb * BN + 8 * lane;
+      for (int rr = warp - 2; rr < rows_cta; rr += 4) {
+        const int r = rank * rows_cta + rr, row = mb * kBM + r;
+        const uint32_t off0 = smem_base + (uint32_t)(rr * (BN / 4) + ((2 * lane) ^ (r & 7))) * 16u;
+        const uint32_t off1 = smem_base + (uint32_t)(rr * (BN / 4) + ((2 * lane + 1) ^ (r & 7))) * 16u;
+        const uint32_t slab = (uint32_t)(rows_cta * (BN / 4)) * 16u;
+        uint32_t v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll 8
+        for (int z = 0; z < ksplit; ++z) {
+          const uint4 p0 = ld_shared_v4(off0 + (uint32_t)z * slab);
+          const uint4 p1 = ld_shared_v4(off1 + (uint32_t)z * slab);
+          v[0] += p0.x; v[1] += p0.y; v[2] += p0.z; v[3] += p0.w;
+          v[4] += p1.x; v[5] += p1.y; v[6] += p1.z; v[7] += p1.w;
+        }
+        if (row < t && col < n) {
+          const float s_row = sa[row];
+          uint32_t w[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            w[j] = pack_out2<OutT>(((float)(int)v[2 * j] * s_row) * sb_s[8 * lane + 2 * j],
+                                   ((float)(int)v[2 * j + 1] * s_row) * sb_s[8 * lane + 2 * j + 1]);
+          if (bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 o = unpack_out2(w[j], OutT());
+              const float2 b = unpack_out2(*reinterpret_cast<const uint32_t*>(bias + col + 2 * j), OutT());
+              w[j] = pack_out2<OutT>(o.x + b.x, o.y + b.y);
+            }
+          }
+          *reinterpret_cast<uint4*>(out + (int64_t)row * n + col) = make_uint4(w[0], w[1], w[2], w[3]);
+          if (acc_out != nullptr) {
+            uint4* arow = reinterpret_cast<uint4*>(acc_out + (int64_t)row * n + col);
+            arow[0] = make_uint4(v[0], v[1], v[2], v[3]);
+            arow[1] = make_uint4(v[4], v[5], v[6], v[7]);
+          }
+        }
+      }
+    }
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -344,7 +441,7 @@ gemm_s8_dual_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
           const uint32_t dst = smem_base + s * C::kStageBytes;
           tma_load_2d(dst, &a_map, bar, ks * kBK, mb * BM2);
           tma_load_2d(dst + kBM * kBK, &a_map, bar, ks * kBK, mb * BM2 + kBM);
-          tma_load_2d(dst + 2 * kBM * kBK, &b_map, bar, ks * kBK, nb * BN);
+          tma_load_2d(dst + 2 * kBM * kBK, &b_map, bar, 0, b_block_row(nb * BN, ks, ksteps));
         }
       }
     }
@@ -437,41 +534,6 @@ gemm_s8_dual_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_cons
   }
 }
 
-// second step of a K-split GEMM: scales (and bias) applied to the summed int32 accumulators, 8 outputs per thread
-// (n is a multiple of 8 on this path)
-template <typename OutT>
-__global__ void __launch_bounds__(256)
-gemm_finish_kernel(const int32_t* __restrict__ part, const float* __restrict__ sa, const float* __restrict__ sb,
-                   OutT* __restrict__ out, int32_t* __restrict__ acc_out, const OutT* __restrict__ bias, int64_t t, int64_t n) {
-  const int64_t n8 = n / 8, total = t * n8;
-  for (int64_t i = blockIdx.x * 256LL + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
-    const int64_t r = i / n8, c = (i - r * n8) * 8;
-    const int4 a0 = *reinterpret_cast<const int4*>(part + r * n + c), a1 = *reinterpret_cast<const int4*>(part + r * n + c + 4);
-    const float4 s0 = *reinterpret_cast<const float4*>(sb + c), s1 = *reinterpret_cast<const float4*>(sb + c + 4);
-    const float s_row = sa[r];
-    const int acc[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-    const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-    uint32_t w[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-      w[j] = pack_out2<OutT>(((float)acc[2 * j] * s_row) * sc[2 * j], ((float)acc[2 * j + 1] * s_row) * sc[2 * j + 1]);
-    if (bias != nullptr) {
-      const uint4 bw = *reinterpret_cast<const uint4*>(bias + c);
-      const uint32_t b[4] = {bw.x, bw.y, bw.z, bw.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 o = unpack_out2(w[j], OutT()), bb = unpack_out2(b[j], OutT());
-        w[j] = pack_out2<OutT>(o.x + bb.x, o.y + bb.y);
-      }
-    }
-    *reinterpret_cast<uint4*>(out + r * n + c) = make_uint4(w[0], w[1], w[2], w[3]);
-    if (acc_out != nullptr) {
-      *reinterpret_cast<int4*>(acc_out + r * n + c) = a0;
-      *reinterpret_cast<int4*>(acc_out + r * n + c + 4) = a1;
-    }
-  }
-}
-
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -503,15 +565,28 @@ int make_map_s8(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int
   return QO_OK;
 }
 
+// the blocked B operand as a matrix of 128-byte rows (256 per block); a box is one slice of box_rows channels
+int make_map_b(CUtensorMap* map, const void* base, int64_t n, int64_t k, int box_rows) {
+  const int64_t rows = ((n + 255) / 256) * ((k + kBK - 1) / kBK) * 256;
+  const cuuint64_t dims[2] = {(cuuint64_t)kBK, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)kBK};
+  const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = gemm_encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(QO_ERR_CUDA, "int4_matmul: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return QO_OK;
+}
+
 template <int BN, typename OutT>
 int launch_gemm_tile(const int8_t* a8, const int8_t* b8, const float* sa, const float* sb, void* out, int32_t* acc_out,
-                     const void* bias, int64_t t, int64_t k, int64_t n, uint32_t* status, cudaStream_t stream, int ksplit = 1,
-                     int32_t* part = nullptr) {
+                     const void* bias, int64_t t, int64_t k, int64_t n, uint32_t* status, cudaStream_t stream, int ksplit = 1) {
   using C = GemmCfg<BN>;
   CUtensorMap a_map, b_map;
   int rc = make_map_s8(&a_map, a8, t, k, kBM);
   if (rc) return rc;
-  if ((rc = make_map_s8(&b_map, b8, n, k, BN))) return rc;
+  if ((rc = make_map_b(&b_map, b8, n, k, BN))) return rc;
   auto kern = gemm_s8_sm100_kernel<BN, OutT>;
   int dev = 0, sms = 148;
   QO_CUDA_TRY(cudaGetDevice(&dev));
@@ -522,20 +597,28 @@ int launch_gemm_tile(const int8_t* a8, const int8_t* b8, const float* sa, const 
   }
   sms = sm_count(dev);
   const int64_t ntiles = ((t + kBM - 1) / kBM) * ((n + BN - 1) / BN) * ksplit;
-  const int grid = (int)(ntiles < sms ? ntiles : sms);
-  if (ksplit > 1) QO_CUDA_TRY(cudaMemsetAsync(part, 0, (size_t)t * n * sizeof(int32_t), stream));
-  kern<<<grid, kGemmThreads, C::kSmemBytes, stream>>>(a_map, b_map, sa, sb, reinterpret_cast<OutT*>(out), acc_out,
-                                                     reinterpret_cast<const OutT*>(bias), (int)t, (int)n, (int)k, ksplit,
-                                                     ksplit > 1 ? part : nullptr, status);
-  if ((rc = check_launch("gemm_s8_sm100_kernel"))) return rc;
+  // K-split: one work item per CTA, the ksplit slices of a tile form a cluster
+  const int grid = (int)((ksplit > 1 || ntiles < sms) ? ntiles : sms);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.numAttrs = 1;
   if (ksplit > 1) {
-    int64_t blocks = (t * (n / 8) + 255) / 256;
-    if (blocks > 148 * 16) blocks = 148 * 16;
-    gemm_finish_kernel<OutT><<<(int)blocks, 256, 0, stream>>>(part, sa, sb, reinterpret_cast<OutT*>(out), acc_out,
-                                                             reinterpret_cast<const OutT*>(bias), t, n);
-    return check_launch("gemm_finish_kernel");
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = (unsigned)ksplit;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
   }
-  return QO_OK;
+  cfg.attrs = attr;
+  QO_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, a_map, b_map, sa, sb, reinterpret_cast<OutT*>(out), acc_out,
+                                 reinterpret_cast<const OutT*>(bias), (int)t, (int)n, (int)k, ksplit, status));
+  return check_launch("gemm_s8_sm100_kernel");
 }
 
 }  // namespace
@@ -546,7 +629,7 @@ int launch_gemm_dual(const int8_t* a8, const int8_t* b8, const float* sa, const 
   CUtensorMap a_map, b_map;
   int rc = make_map_s8(&a_map, a8, t, k, kBM);
   if (rc) return rc;
-  if ((rc = make_map_s8(&b_map, b8, n, k, 256))) return rc;
+  if ((rc = make_map_b(&b_map, b8, n, k, 256))) return rc;
   auto kern = gemm_s8_dual_kernel<OutT>;
   int dev = 0;
   QO_CUDA_TRY(cudaGetDevice(&dev));
@@ -563,29 +646,61 @@ int launch_gemm_dual(const int8_t* a8, const int8_t* b8, const float* sa, const 
   return check_launch("gemm_s8_dual_kernel");
 }
 
-// K slices per output tile: few 128 x 256 tiles (a short activation matrix) leave most SMs idle and small tiles
-// re-read the activations once per column tile, so the tiles stay wide and K is split instead.
+// K slices per output tile (1, 2, 4 or 8: the slices of a tile form a thread-block cluster): few 128 x 256 tiles (a
+// short activation matrix) leave most SMs idle and small tiles re-read the activations once per column tile, so the
+// tiles stay wide and K is split instead.
 int gemm_k_split(int64_t t, int64_t k, int64_t n) {
   if (n < 256) return 1;
   const int64_t tiles = ((t + kBM - 1) / kBM) * ((n + 255) / 256), ksteps = (k + kBK - 1) / kBK;
   if (tiles >= 120) return 1;
-  int64_t split = 148 / tiles;
-  if (split > 8) split = 8;
-  if (split > ksteps / 8) split = ksteps / 8;
-  return split >= 2 ? (int)split : 1;
+  int64_t limit = 148 / tiles;
+  if (limit > ksteps / 8) limit = ksteps / 8;
+  int split = 1;
+  while (split * 2 <= limit && split < 8) split *= 2;
+  return split;
 }
 
 namespace {
 
+// How many clusters of `size` CTAs of the K-split kernel the device runs at once (0 if the query fails); cached.
+template <typename OutT>
+int max_split_clusters(int dev, int size) {
+  static int cached[64][4] = {};  // [device][log2(size)], 0 = not asked yet, -1 = failed
+  const int lg = size == 8 ? 3 : (size == 4 ? 2 : 1);
+  int& c = cached[dev & 63][lg];
+  if (c == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(size * 64));
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = GemmCfg<256>::kSmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)size;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    (void)cudaFuncSetAttribute(gemm_s8_sm100_kernel<256, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<256>::kSmemBytes);
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_s8_sm100_kernel<256, OutT>, &cfg) != cudaSuccess) { (void)cudaGetLastError(); n = -1; }
+    c = n > 0 ? n : -1;
+  }
+  return c > 0 ? c : 0;
+}
+
 template <typename OutT>
 int launch_gemm_typed(const int8_t* a8, const int8_t* b8, const float* sa, const float* sb, void* out, int32_t* acc_out,
-                      const void* bias, int64_t t, int64_t k, int64_t n, uint32_t* status, cudaStream_t stream,
-                      int32_t* part = nullptr) {
-  // the finishing kernel of a K-split reads scale_b and bias 16 bytes at a time
-  const bool vec_ok = reinterpret_cast<uintptr_t>(sb) % 16 == 0 && (bias == nullptr || reinterpret_cast<uintptr_t>(bias) % 16 == 0);
-  const int ksplit = (part != nullptr && vec_ok) ? gemm_k_split(t, k, n) : 1;
+                      const void* bias, int64_t t, int64_t k, int64_t n, uint32_t* status, cudaStream_t stream) {
+  int ksplit = gemm_k_split(t, k, n);
+  if (ksplit > 1) {
+    // all clusters of a launch should run at once: a second wave would double the time
+    int dev = 0;
+    QO_CUDA_TRY(cudaGetDevice(&dev));
+    const int64_t tiles = ((t + kBM - 1) / kBM) * ((n + 255) / 256);
+    while (ksplit > 1 && max_split_clusters<OutT>(dev, ksplit) < tiles) ksplit /= 2;
+  }
   if (ksplit > 1)
-    return launch_gemm_tile<256, OutT>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, ksplit, part);
+    return launch_gemm_tile<256, OutT>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, ksplit);
   // enough 256 x 256 tiles for every SM: two accumulators per CTA share each B slice
   // (with few tiles and a short K the unshared tile does better: its epilogue overlaps the next main loop and its
   // smaller tiles fill the last wave more evenly)
@@ -605,10 +720,15 @@ inline size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 
 }  // namespace
 
+// bytes of the blocked int8 B operand: whole blocks of 256 channels x 128 K-bytes
+size_t gemm_b8_bytes(int64_t n, int64_t k) {
+  if (n <= 0 || k <= 0) return 0;
+  return (size_t)((n + 255) / 256) * (size_t)((k + kBK - 1) / kBK) * (size_t)(256 * kBK);
+}
+
 size_t gemm_sm100_workspace_bytes(int64_t t, int64_t k, int64_t n) {
   if (t <= 0 || k <= 0 || n <= 0) return 0;
-  const size_t part = gemm_k_split(t, k, n) > 1 ? align256((size_t)t * n * sizeof(int32_t)) : 0;  // K-split partial sums
-  return align256((size_t)t * k) + align256((size_t)n * k) + part;
+  return align256((size_t)t * k) + gemm_b8_bytes(n, k);
 }
 
 bool gemm_sm100_supported(int64_t t, int64_t k, int64_t n, int64_t lda, int64_t bsk, int64_t bsn) {
@@ -616,12 +736,13 @@ bool gemm_sm100_supported(int64_t t, int64_t k, int64_t n, int64_t lda, int64_t 
   if (k % 16 || k < 16) return false;              // TMA: row stride of the widened operands must be 16-byte aligned
   if (n % 8) return false;                         // 16-byte output stores
   if (t > 0x7fffff00LL || n > 0x7fffff00LL || k > 262143) return false;
+  if (((n + 255) / 256) * ((k + kBK - 1) / kBK) * 256 > 0x7fffff00LL) return false;  // 128-byte rows of the blocked B operand (TMA coordinate)
   if (bsk != 1 && bsn != 1) return false;
   return gemm_encode_fn() != nullptr;
 }
 
 int launch_gemm_sm100_s8(const int8_t* a8, const int8_t* b8, const float* sa, const float* sb, void* out, int out_dtype,
-                         int64_t t, int64_t k, int64_t n, int32_t* acc_out, const void* bias, cudaStream_t stream, int32_t* part) {
+                         int64_t t, int64_t k, int64_t n, int32_t* acc_out, const void* bias, cudaStream_t stream) {
   if (reinterpret_cast<uintptr_t>(a8) % 16 || reinterpret_cast<uintptr_t>(b8) % 16 || reinterpret_cast<uintptr_t>(out) % 16 ||
       (acc_out && reinterpret_cast<uintptr_t>(acc_out) % 16) || (bias && reinterpret_cast<uintptr_t>(bias) % 4))
     return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: operands of the tcgen05 kernel must be 16-byte aligned");
@@ -629,14 +750,16 @@ int launch_gemm_sm100_s8(const int8_t* a8, const int8_t* b8, const float* sa, co
   QO_CUDA_TRY(cudaGetDevice(&dev));
   uint32_t* status = device_status_word(dev);
   if (!status) return fail(QO_ERR_CUDA, "int4_matmul: could not allocate the device status word");
-  if (out_dtype == QO_F16) return launch_gemm_typed<__half>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, part);
-  return launch_gemm_typed<__nv_bfloat16>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, part);
+  if (out_dtype == QO_F16) return launch_gemm_typed<__half>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream);
+  return launch_gemm_typed<__nv_bfloat16>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream);
 }
 
-int launch_widen_rows(const int32_t* in, int64_t ld_words, int8_t* out, int64_t rows, int64_t k, cudaStream_t stream) {
+// blocked: write the layout of the B operand (see the head of this file) instead of row-major
+int launch_widen_rows(const int32_t* in, int64_t ld_words, int8_t* out, int64_t rows, int64_t k, cudaStream_t stream, bool blocked) {
+  const int64_t ksteps = blocked ? (k + kBK - 1) / kBK : 0;
   if ((k % 32) == 0 && (ld_words % 4) == 0 && reinterpret_cast<uintptr_t>(in) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) {
-    const WidenJob job = {reinterpret_cast<const uint32_t*>(in), reinterpret_cast<uint4*>(out), ld_words, rows, k / 32};
-    const WidenJob none = {nullptr, nullptr, 0, 0, 1};
+    const WidenJob job = {reinterpret_cast<const uint32_t*>(in), reinterpret_cast<uint8_t*>(out), ld_words, rows, k / 32, ksteps};
+    const WidenJob none = {nullptr, nullptr, 0, 0, 1, 0};
     int64_t blocks = (rows * (k / 32) + 255) / 256;
     if (blocks > 148 * 32) blocks = 148 * 32;
     if (blocks < 1) blocks = 1;
@@ -647,7 +770,7 @@ int launch_widen_rows(const int32_t* in, int64_t ld_words, int8_t* out, int64_t 
   int64_t blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   widen_rows_kernel<<<(int)blocks, 256, 0, stream>>>(reinterpret_cast<const uint32_t*>(in), ld_words,
-                                                     reinterpret_cast<uint2*>(out), rows, k / 8);
+                                                     reinterpret_cast<uint8_t*>(out), rows, k / 8, ksteps);
   return check_launch("widen_rows_kernel");
 }
 
@@ -658,40 +781,39 @@ int launch_gemm_sm100(const int32_t* a, int64_t lda, const int32_t* b, int64_t b
     return fail(QO_ERR_WORKSPACE, "int4_matmul: workspace missing, too small or not 256-byte aligned");
   int8_t* a8 = reinterpret_cast<int8_t*>(workspace);
   int8_t* b8 = a8 + align256((size_t)t * k);
-  int32_t* part = gemm_k_split(t, k, n) > 1 ? reinterpret_cast<int32_t*>(b8 + align256((size_t)n * k)) : nullptr;
   int rc;
   if (bsk == 1 && (k % 32) == 0 && (lda % 4) == 0 && (bsn % 4) == 0 && reinterpret_cast<uintptr_t>(a) % 16 == 0 &&
       reinterpret_cast<uintptr_t>(b) % 16 == 0) {
     // both operands have K contiguous and 16-byte aligned rows: one launch widens both
-    const WidenJob ja = {reinterpret_cast<const uint32_t*>(a), reinterpret_cast<uint4*>(a8), lda, t, k / 32};
-    const WidenJob jb = {reinterpret_cast<const uint32_t*>(b), reinterpret_cast<uint4*>(b8), bsn, n, k / 32};
+    const WidenJob ja = {reinterpret_cast<const uint32_t*>(a), reinterpret_cast<uint8_t*>(a8), lda, t, k / 32, 0};
+    const WidenJob jb = {reinterpret_cast<const uint32_t*>(b), reinterpret_cast<uint8_t*>(b8), bsn, n, k / 32, (k + kBK - 1) / kBK};
     const int64_t total = (t + n) * (k / 32);
     int64_t blocks = (total + 255) / 256;
     if (blocks > 148 * 32) blocks = 148 * 32;
     widen_rows2_kernel<<<(int)blocks, 256, 0, stream>>>(ja, jb);
     if ((rc = check_launch("widen_rows2_kernel"))) return rc;
-    return launch_gemm_sm100_s8(a8, b8, sa, sb, out, out_dtype, t, k, n, acc_out, bias, stream, part);
+    return launch_gemm_sm100_s8(a8, b8, sa, sb, out, out_dtype, t, k, n, acc_out, bias, stream);
   }
-  rc = launch_widen_rows(a, lda, a8, t, k, stream);
+  rc = launch_widen_rows(a, lda, a8, t, k, stream, false);
   if (rc) return rc;
   if (bsk == 1) {
-    rc = launch_widen_rows(b, bsn, b8, n, k, stream);  // rows of the weight matrix [Nout, K/8]
+    rc = launch_widen_rows(b, bsn, b8, n, k, stream, true);  // rows of the weight matrix [Nout, K/8]
   } else {
     dim3 grid((unsigned)((n + 31) / 32), (unsigned)((k / 8 + 31) / 32));
     widen_transpose_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const uint32_t*>(b), bsk, bsn,
-                                                     reinterpret_cast<uint2*>(b8), n, k / 8);
+                                                     reinterpret_cast<uint8_t*>(b8), n, k / 8, (k + kBK - 1) / kBK);
     rc = check_launch("widen_transpose_kernel");
   }
   if (rc) return rc;
-  return launch_gemm_sm100_s8(a8, b8, sa, sb, out, out_dtype, t, k, n, acc_out, bias, stream, part);
+  return launch_gemm_sm100_s8(a8, b8, sa, sb, out, out_dtype, t, k, n, acc_out, bias, stream);
 }
 
 // ---- pieces for callers that bring their own scratch and status word (int4_gemm_static.cu) ------------------------
 int launch_widen_b(const int32_t* b, int64_t bsk, int64_t bsn, int8_t* b8, int64_t n, int64_t k, cudaStream_t stream) {
-  if (bsk == 1) return launch_widen_rows(b, bsn, b8, n, k, stream);
+  if (bsk == 1) return launch_widen_rows(b, bsn, b8, n, k, stream, true);
   dim3 grid((unsigned)((n + 31) / 32), (unsigned)((k / 8 + 31) / 32));
   widen_transpose_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const uint32_t*>(b), bsk, bsn,
-                                                   reinterpret_cast<uint2*>(b8), n, k / 8);
+                                                   reinterpret_cast<uint8_t*>(b8), n, k / 8, (k + kBK - 1) / kBK);
   return check_launch("widen_transpose_kernel");
 }
 

@@ -17,7 +17,7 @@
 namespace qo {
 namespace {
 
-constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB: tokens*k + n_out*k bytes must fit (plus 256-byte rounding)
+constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB: tokens*k bytes + the blocked int8 weights (whole 256 x 128 blocks) must fit
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 static __device__ __align__(256) uint32_t g_static_status[64];
@@ -75,9 +75,9 @@ int qo_int4_matmul_static(const int32_t* a, int64_t lda, const int32_t* b, int64
   if (k % 8 || lda < k / 8) return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul_static: k must be a multiple of 8 and lda >= k/8");
   if (!gemm_sm100_supported(tokens, k, n_out, lda, b_stride_k, b_stride_n))
     return fail(QO_ERR_UNSUPPORTED, "int4_matmul_static: only the shapes of the tcgen05 kernel are served here (k %% 16 == 0, n_out %% 8 == 0, unit stride along k or n_out); got t=%lld k=%lld n=%lld", (long long)tokens, (long long)k, (long long)n_out);
-  const size_t a_bytes = align256((size_t)tokens * (size_t)k), need = a_bytes + align256((size_t)n_out * (size_t)k);
+  const size_t a_bytes = align256((size_t)tokens * (size_t)k), need = a_bytes + gemm_b8_bytes(n_out, k);
   if (need > kStaticScratchBytes)
-    return fail(QO_ERR_WORKSPACE, "int4_matmul_static: tokens*k + n_out*k = %zu bytes exceeds the built-in scratch of %zu bytes; use qo_int4_matmul with a workspace", need, (size_t)kStaticScratchBytes);
+    return fail(QO_ERR_WORKSPACE, "int4_matmul_static: the widened operands take %zu bytes, which exceeds the built-in scratch of %zu bytes; use qo_int4_matmul with a workspace", need, (size_t)kStaticScratchBytes);
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) {
@@ -94,7 +94,7 @@ int qo_int4_matmul_static(const int32_t* a, int64_t lda, const int32_t* b, int64
   int8_t* a8 = reinterpret_cast<int8_t*>(addr.scratch);
   int8_t* b8 = a8 + a_bytes;
   // every byte the GEMM reads is rewritten by the two widen passes, so nothing has to be cleared between calls
-  if ((rc = launch_widen_rows(a, lda, a8, tokens, k, st))) return rc;
+  if ((rc = launch_widen_rows(a, lda, a8, tokens, k, st, false))) return rc;
   if ((rc = launch_widen_b(b, b_stride_k, b_stride_n, b8, n_out, k, st))) return rc;
   return launch_gemm_sm100_s8_status(a8, b8, scale_a, scale_b, out, out_dtype, tokens, k, n_out, nullptr, addr.status, st);
 }

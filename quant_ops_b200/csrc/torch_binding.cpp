@@ -169,7 +169,7 @@ at::Tensor prepare_weights(const at::Tensor& w_packed) {
   c10::cuda::CUDAGuard guard(w_packed.device());
   at::Tensor w = w_packed.contiguous();
   const int64_t n_out = w.size(0), k = w.size(1) * 8;
-  at::Tensor out = at::empty({n_out, k}, w.options().dtype(at::kChar));
+  at::Tensor out = at::empty({(int64_t)qo_prepared_weights_bytes(n_out, k)}, w.options().dtype(at::kByte));
   check_status(qo_prepare_weights(w.data_ptr<int32_t>(), out.data_ptr(), n_out, k, current_stream()), "prepare_weights");
   return out;
 }
@@ -187,9 +187,9 @@ at::Tensor w4a4_linear_prepared(const at::Tensor& x, const at::Tensor& left_tran
               "w4a4_linear_prepared: transforms must have the dtype of x");
   TORCH_CHECK(w_packed.dim() == 2 && w_packed.scalar_type() == at::kInt && w_packed.size(1) * 8 == k,
               "w4a4_linear_prepared: w_packed must be int32 [n_out, K/8]");
-  TORCH_CHECK(w_prepared.dim() == 2 && w_prepared.scalar_type() == at::kChar && w_prepared.size(0) == w_packed.size(0) &&
-                  w_prepared.size(1) == k && w_prepared.is_contiguous(),
-              "w4a4_linear_prepared: w_prepared must be the contiguous int8 [n_out, K] tensor made by prepare_weights");
+  TORCH_CHECK(w_prepared.dim() == 1 && w_prepared.scalar_type() == at::kByte && w_prepared.is_contiguous() &&
+                  w_prepared.numel() == (int64_t)qo_prepared_weights_bytes(w_packed.size(0), k),
+              "w4a4_linear_prepared: w_prepared must be the byte tensor made by prepare_weights for these weights");
   TORCH_CHECK(w_scale.scalar_type() == at::kFloat && w_scale.numel() == w_packed.size(0),
               "w4a4_linear_prepared: w_scale must be float32 [n_out]");
   const at::ScalarType out_dtype = out_dtype_opt.has_value() ? *out_dtype_opt : (x.scalar_type() == at::kBFloat16 ? at::kBFloat16 : at::kHalf);

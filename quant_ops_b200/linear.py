@@ -19,8 +19,8 @@ from .decompose import get_decompose_dim
 class W4A4Linear(torch.nn.Module):
     def __init__(self, in_features: int, out_features: int, bias: bool = False, clip_ratio: float = 1.0,
                  dtype: torch.dtype = torch.bfloat16, device=None, keep_int8_weights: bool = False):
-        """keep_int8_weights: also hold the weights widened to int8 [out, in] (twice the packed size); forward then
-        rewrites no operand per call.  The copy is made by load_quantized / load_float / prepare()."""
+        """keep_int8_weights: also hold the weights widened to int8 in the GEMM's blocked layout (a byte tensor, about
+        twice the packed size); forward then rewrites no operand per call.  The copy is made by load_quantized / load_float / prepare()."""
         super().__init__()
         self.keep_int8_weights = bool(keep_int8_weights)
         self.weight_int8 = None  # derived from weight_packed, not part of the state dict

@@ -50,7 +50,8 @@ def _linear_fake(x, left_trans, right_trans, w_packed, w_scale, bias=None, clip_
 
 @register_fake("quant_ops::prepare_weights")
 def _prepare_fake(w_packed):
-    return w_packed.new_empty((w_packed.size(0), w_packed.size(1) * 8), dtype=torch.int8)
+    blocks = ((w_packed.size(0) + 255) // 256) * ((w_packed.size(1) * 8 + 127) // 128)
+    return w_packed.new_empty((blocks * 256 * 128,), dtype=torch.uint8)
 
 
 @register_fake("quant_ops::w4a4_linear_prepared")

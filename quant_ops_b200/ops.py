@@ -59,7 +59,8 @@ def w4a4_linear(x: torch.Tensor, left_trans: torch.Tensor, right_trans: torch.Te
 
 
 def prepare_weights(w_packed: torch.Tensor) -> torch.Tensor:
-    """Packed weights [n_out, K/8] -> int8 [n_out, K], widened once at load time for w4a4_linear_prepared."""
+    """Packed weights [n_out, K/8] -> the int8 operand of the tensor-core GEMM (a byte tensor in the kernel's blocked
+    layout: 256 output channels x 128 values per 32 KB block), made once at load time for w4a4_linear_prepared."""
     return _ops.prepare_weights(w_packed)
 
 

@@ -107,8 +107,11 @@ def test_prepared_weights_give_identical_results(tokens, k, n_out):
     plain.load_float(w, left.to(DEV), right.to(DEV), bias)
     kept = q.W4A4Linear(k, n_out, bias=True, clip_ratio=0.9, dtype=torch.bfloat16, device=DEV, keep_int8_weights=True)
     kept.load_float(w, left.to(DEV), right.to(DEV), bias)
-    assert kept.weight_int8 is not None and kept.weight_int8.shape == (n_out, k)
-    assert torch.equal(kept.weight_int8, q.unpack_int32_to_int4(kept.weight_packed))
+    # the kept copy is the GEMM's int8 operand: blocks of 256 output channels x 128 values, ordered [n_out/256][k/128]
+    nb, ks = (n_out + 255) // 256, (k + 127) // 128
+    assert kept.weight_int8 is not None and kept.weight_int8.shape == (nb * ks * 256 * 128,)
+    rows = kept.weight_int8.view(torch.int8).view(nb, ks, 256, 128).permute(0, 2, 1, 3).reshape(nb * 256, ks * 128)
+    assert torch.equal(rows[:n_out, :k], q.unpack_int32_to_int4(kept.weight_packed))
     y0, y1 = plain(x.to(DEV)), kept(x.to(DEV))
     assert torch.equal(y0, y1)
     assert N.lib.qo_device_status(C.c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
