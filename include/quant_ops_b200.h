@@ -174,7 +174,8 @@ QO_API int qo_w4a4_linear(const void* x, int64_t ldx, const void* left, const vo
 
 /*
  * Layer form with weights prepared once.  The weights of a layer do not change between calls, so a host that can
- * spend k bytes per output channel keeps them widened to int8 [n_out, k] (qo_prepare_weights, at load time) and the
+ * spend about k bytes per output channel keeps them widened to int8 (qo_prepare_weights, at load time; the buffer is
+ * opaque: the GEMM's own layout, blocks of 256 output channels x 128 values, padded to whole blocks) and the
  * per-call work shrinks to: quantize the activations straight to int8 codes, then the tensor-core GEMM; no operand
  * is rewritten per call.  Results are identical to qo_w4a4_linear.  Calls with at most 32 tokens read the packed
  * weights instead (half the bytes), so both buffers are passed.
