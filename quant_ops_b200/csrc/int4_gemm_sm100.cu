@@ -333,11 +333,13 @@ gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_con
       const int mb = tile / tiles_n, nb = tile - mb * tiles_n;
       const int rows_cta = kBM / ksplit;
       const float* sb_s = reinterpret_cast<float*>(smem + C::kOffSb) + (warp - 2) * BN;  // this warp's copy, filled above
-      const int col = nb * BN + 8 * lane;
-      for (int rr = warp - 2; rr < rows_cta; rr += 4) {
+      constexpr int kLanesPerRow = BN / 8, kRowsPerPass = 32 / kLanesPerRow;  // a warp covers 1, 2 or 4 rows at a time
+      const int cl = lane % kLanesPerRow;
+      const int col = nb * BN + 8 * cl;
+      for (int rr = (warp - 2) * kRowsPerPass + lane / kLanesPerRow; rr < rows_cta; rr += 4 * kRowsPerPass) {
         const int r = rank * rows_cta + rr, row = mb * kBM + r;
-        const uint32_t off0 = smem_base + (uint32_t)(rr * (BN / 4) + ((2 * lane) ^ (r & 7))) * 16u;
-        const uint32_t off1 = smem_base + (uint32_t)(rr * (BN / 4) + ((2 * lane + 1) ^ (r & 7))) * 16u;
+        const uint32_t off0 = smem_base + (uint32_t)(rr * (BN / 4) + ((2 * cl) ^ (r & 7))) * 16u;
+        const uint32_t off1 = smem_base + (uint32_t)(rr * (BN / 4) + ((2 * cl + 1) ^ (r & 7))) * 16u;
         const uint32_t slab = (uint32_t)(rows_cta * (BN / 4)) * 16u;
         uint32_t v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll 8
@@ -352,8 +354,8 @@ gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_con
           uint32_t w[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j)
-            w[j] = pack_out2<OutT>(((float)(int)v[2 * j] * s_row) * sb_s[8 * lane + 2 * j],
-                                   ((float)(int)v[2 * j + 1] * s_row) * sb_s[8 * lane + 2 * j + 1]);
+            w[j] = pack_out2<OutT>(((float)(int)v[2 * j] * s_row) * sb_s[8 * cl + 2 * j],
+                                   ((float)(int)v[2 * j + 1] * s_row) * sb_s[8 * cl + 2 * j + 1]);
           if (bias != nullptr) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -646,24 +648,11 @@ int launch_gemm_dual(const int8_t* a8, const int8_t* b8, const float* sa, const 
   return check_launch("gemm_s8_dual_kernel");
 }
 
-// K slices per output tile (1, 2, 4 or 8: the slices of a tile form a thread-block cluster): few 128 x 256 tiles (a
-// short activation matrix) leave most SMs idle and small tiles re-read the activations once per column tile, so the
-// tiles stay wide and K is split instead.
-int gemm_k_split(int64_t t, int64_t k, int64_t n) {
-  if (n < 256) return 1;
-  const int64_t tiles = ((t + kBM - 1) / kBM) * ((n + 255) / 256), ksteps = (k + kBK - 1) / kBK;
-  if (tiles >= 120) return 1;
-  int64_t limit = 148 / tiles;
-  if (limit > ksteps / 8) limit = ksteps / 8;
-  int split = 1;
-  while (split * 2 <= limit && split < 8) split *= 2;
-  return split;
-}
-
 namespace {
 
-// How many clusters of `size` CTAs of the K-split kernel the device runs at once (0 if the query fails); cached.
-template <typename OutT>
+// How many clusters of `size` CTAs of the K-split kernel with BN-wide tiles the device runs at once (0 if the query
+// fails); cached.
+template <int BN, typename OutT>
 int max_split_clusters(int dev, int size) {
   static int cached[64][4] = {};  // [device][log2(size)], 0 = not asked yet, -1 = failed
   const int lg = size == 8 ? 3 : (size == 4 ? 2 : 1);
@@ -672,7 +661,7 @@ int max_split_clusters(int dev, int size) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(size * 64));
     cfg.blockDim = dim3(kGemmThreads);
-    cfg.dynamicSmemBytes = GemmCfg<256>::kSmemBytes;
+    cfg.dynamicSmemBytes = GemmCfg<BN>::kSmemBytes;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = (unsigned)size;
@@ -681,23 +670,43 @@ int max_split_clusters(int dev, int size) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n = 0;
-    (void)cudaFuncSetAttribute(gemm_s8_sm100_kernel<256, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<256>::kSmemBytes);
-    if (cudaOccupancyMaxActiveClusters(&n, gemm_s8_sm100_kernel<256, OutT>, &cfg) != cudaSuccess) { (void)cudaGetLastError(); n = -1; }
+    (void)cudaFuncSetAttribute(gemm_s8_sm100_kernel<BN, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::kSmemBytes);
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_s8_sm100_kernel<BN, OutT>, &cfg) != cudaSuccess) { (void)cudaGetLastError(); n = -1; }
     c = n > 0 ? n : -1;
   }
   return c > 0 ? c : 0;
 }
 
+// K slices per output tile of 128 x BN (1, 2, 4 or 8: the slices of a tile form a thread-block cluster).  Few tiles (a
+// short activation matrix) leave most SMs idle and small tiles re-read the activations once per column tile, so the
+// tiles stay wide and K is split instead.  All clusters of a launch should run at once (a second wave would double
+// the time), so the split is lowered until the device says they do.
+template <int BN, typename OutT>
+int gemm_k_split(int dev, int64_t t, int64_t k, int64_t n) {
+  if (n < BN) return 1;
+  const int64_t tiles = ((t + kBM - 1) / kBM) * ((n + BN - 1) / BN), ksteps = (k + kBK - 1) / kBK;
+  if (tiles >= 120) return 1;
+  int64_t limit = 148 / tiles;
+  if (limit > ksteps / 8) limit = ksteps / 8;
+  int split = 1;
+  while (split * 2 <= limit && split < 8) split *= 2;
+  while (split > 1 && max_split_clusters<BN, OutT>(dev, split) < tiles) split /= 2;
+  return split;
+}
+
 template <typename OutT>
 int launch_gemm_typed(const int8_t* a8, const int8_t* b8, const float* sa, const float* sb, void* out, int32_t* acc_out,
                       const void* bias, int64_t t, int64_t k, int64_t n, uint32_t* status, cudaStream_t stream) {
-  int ksplit = gemm_k_split(t, k, n);
-  if (ksplit > 1) {
-    // all clusters of a launch should run at once: a second wave would double the time
-    int dev = 0;
-    QO_CUDA_TRY(cudaGetDevice(&dev));
-    const int64_t tiles = ((t + kBM - 1) / kBM) * ((n + 255) / 256);
-    while (ksplit > 1 && max_split_clusters<OutT>(dev, ksplit) < tiles) ksplit /= 2;
+  int dev = 0;
+  QO_CUDA_TRY(cudaGetDevice(&dev));
+  const int ksplit = gemm_k_split<256, OutT>(dev, t, k, n);
+  if (t <= kBM) {
+    // one row block: tiles half as wide put twice as many CTAs to work when the wide ones leave half the SMs idle
+    const int64_t ctas256 = ((n + 255) / 256) * ksplit;
+    const int ksplit128 = gemm_k_split<128, OutT>(dev, t, k, n);
+    const int64_t ctas128 = ((n + 127) / 128) * ksplit128;
+    if (ksplit128 > 1 && ctas256 <= 74 && ctas128 > ctas256)
+      return launch_gemm_tile<128, OutT>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, ksplit128);
   }
   if (ksplit > 1)
     return launch_gemm_tile<256, OutT>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, ksplit);

@@ -165,7 +165,6 @@ int launch_gemm_skinny(const int32_t* a, int64_t lda, const int32_t* b, int64_t 
                        int out_dtype, int64_t t, int64_t k, int64_t n, int32_t* acc_out, const void* bias, cudaStream_t stream,
                        bool weights_first = false);
 size_t gemm_sm100_workspace_bytes(int64_t t, int64_t k, int64_t n);
-int gemm_k_split(int64_t t, int64_t k, int64_t n);  // K slices per output tile the tcgen05 GEMM uses for this shape (1 = none)
 bool gemm_sm100_supported(int64_t t, int64_t k, int64_t n, int64_t lda, int64_t bsk, int64_t bsn);
 int launch_gemm_sm100(const int32_t* a, int64_t lda, const int32_t* b, int64_t bsk, int64_t bsn,
                       const float* sa, const float* sb, void* out, int out_dtype, int64_t t, int64_t k,

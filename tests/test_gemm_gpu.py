@@ -51,7 +51,7 @@ SHAPES = [(1, 64, 8), (1, 4096, 4096), (16, 14336, 512), (128, 256, 256), (129, 
           # 512 tiles of 128 x 256 on 148 SMs, exact and with a ragged last column tile
           (4096, 256, 4096), (4096, 256, 3848),
           # K split over several CTAs per tile: 8 slices of 3 tiles, 2 slices of 8 ragged tiles
-          (64, 8192, 768), (200, 2048, 1000)]
+          (64, 8192, 768), (200, 2048, 1000), (100, 4096, 1000)]
 
 
 @pytest.mark.parametrize("t,k,n", SHAPES)
