@@ -1,14 +1,16 @@
 // FlatQuant quantizer for sm_100a, right transform of size 80, 96, 112 or 128 (features = M x N, 16 <= M <= 128): the
 // hidden sizes 14336 = 112 x 128, 11008 = 86 x 128, 8192 = 64 x 128, 7168 = 64 x 112, 6144 = 64 x 96, 5120 = 64 x 80
 // run here.  For N < 128 everything is laid out as for N = 128: the TMA fills the missing columns of X with zeros,
-// R^T is staged with zero rows and columns, so the extra columns of Y and Z are exact zeros; they are not stored.
+// R is staged with zero columns, so the extra columns of Y and Z are exact zeros; they are not stored.
 //
 // One persistent CTA per SM works on tiles of G tokens: G = 2 when M <= 64 and M is a multiple of 16, else G = 1.
 //
 //   warp 0       TMA: 3-D tensor map (n, m, token), two boxes of 64 x M x G per tile (the two 64-column halves of the
 //                rows), 128-byte swizzle, 2 stages
-//   warp 1       issues Y = X . R        A = X rows (K-major), B = R^T (K-major), M = 128, N = 128, K = 128
-//   warp 2       issues Z = LL . Y       A = LL (K-major): L^T in rows 0 .. M-1, and for G = 2 a second copy below it;
+//   warp 1       issues Y = X . R        A = X rows (K-major), B = R as it lies in memory (N-major), M = 128, N = 128,
+//                                        K = 128
+//   warp 2       issues Z = LL . Y       A = LL: L^T in rows 0 .. M-1, and for G = 2 a second copy below it, staged as
+//                                        the rows of L laid along M (M-major): neither transform is transposed;
 //                                        B = Y (N-major).  G = 1: N = 128.  G = 2: one MMA of N = 256 per K step, the
 //                                        64-column blocks of both tokens interleaved along N, K = M
 //   warps 3-10   Y pass: tensor memory -> round to the activation dtype -> shared memory in the B layout;
@@ -115,59 +117,38 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
   grid_launch_dependents();
 
   if (warp != 0) {
+    // Both transforms are staged as they lie in memory, 16 bytes at a time with the 128-byte XOR swizzle: the tensor
+    // core reads R as an N-major B operand (row k of R = 128-byte rows of the two 64-column blocks) and L as an
+    // M-major A operand (row k of L laid along M, once per token copy), so nothing is transposed here.
     constexpr int kStagers = kThreads - 32;
     const int t13 = tid - 32;
-    // raw copies of L and R into the (still unused) Y stages, all 16-byte loads in flight at once
-    uint16_t* raw_l = reinterpret_cast<uint16_t*>(smem + kOffY);
-    uint16_t* raw_r = reinterpret_cast<uint16_t*>(smem + kOffY + kStageBytes);
-    {
-      const int l_chunks = (m * m) / 8, r_chunks = nc * nc / 8;
-      constexpr int kMaxIter = (2 * 128 * 128 / 8 + kStagers - 1) / kStagers;
-      uint4 tmp[kMaxIter];
-#pragma unroll
-      for (int i = 0; i < kMaxIter; ++i) {
-        const int c = t13 + i * kStagers;
-        if (c < l_chunks) tmp[i] = reinterpret_cast<const uint4*>(left)[c];
-        else if (c - l_chunks < r_chunks) tmp[i] = reinterpret_cast<const uint4*>(right)[c - l_chunks];
-      }
-#pragma unroll
-      for (int i = 0; i < kMaxIter; ++i) {
-        const int c = t13 + i * kStagers;
-        if (c < l_chunks) reinterpret_cast<uint4*>(raw_l)[c] = tmp[i];
-        else if (c - l_chunks < r_chunks) reinterpret_cast<uint4*>(raw_r)[c - l_chunks] = tmp[i];
-      }
-      for (int i = l_chunks * 8 + t13; i < m * m; i += kStagers) raw_l[i] = reinterpret_cast<const uint16_t*>(left)[i];  // m * m not a multiple of 8
+    // R: rows k < nc, 16 pieces per row; columns past nc are zero (the first product always has N = 128)
+    for (int idx = t13; idx < nc * 16; idx += kStagers) {
+      const int k = idx >> 4, c = idx & 15;
+      uint4 w = make_uint4(0, 0, 0, 0);
+      if (8 * c < nc) w = *reinterpret_cast<const uint4*>(right + k * nc + 8 * c);
+      *reinterpret_cast<uint4*>(smem + kOffR + (c >> 3) * kAtomBytes + k * 128 + (((c & 7) ^ (k & 7)) << 4)) = w;
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(kStagers) : "memory");
-    // R^T, K-major: row = output column n; its 16-byte chunk jc holds R[8jc .. 8jc+7][n].  Lanes walk n, so the
-    // 2-byte reads of a warp are contiguous and each thread makes one 16-byte swizzled store.
-    for (int idx = t13; idx < 128 * 16; idx += kStagers) {
-      const int n = idx & 127, jc = idx >> 7;
-      uint32_t w[4] = {0, 0, 0, 0};  // rows and columns past N stay zero
-      if (n < nc && 8 * jc < nc) {
-#pragma unroll
-        for (int e2 = 0; e2 < 4; ++e2)
-          w[e2] = (uint32_t)raw_r[(8 * jc + 2 * e2) * nc + n] | ((uint32_t)raw_r[(8 * jc + 2 * e2 + 1) * nc + n] << 16);
-      }
-      *reinterpret_cast<uint4*>(smem + kOffR + (jc >> 3) * kAtomBytes + (n >> 3) * 1024 + (n & 7) * 128 + (((jc & 7) ^ (n & 7)) << 4)) =
-          make_uint4(w[0], w[1], w[2], w[3]);
-    }
-    // LL, K-major: row (copy, i) = copy * mpad + i, column k holds L[k][i]; all other rows and the columns past m are zero
+    // LL: rows k < k2 (rows m .. k2-1 pad the reduction length and must be zero), M position copy * mpad + i holds
+    // L[k][i]; every other M position of these rows is zero
     const int mpad = (m + 31) & ~31;  // the second copy starts on a 32-row boundary: a warp reads one token's columns
-    for (int idx = t13; idx < 128 * 16; idx += kStagers) {
-      const int r = idx & 127, kc = idx >> 7;
-      const int cpy = r / mpad, i = r - cpy * mpad;
-      const bool row_ok = cpy < group && i < m;
-      uint32_t w[4];
+    const bool l_vec = (m & 7) == 0;  // rows of L start on 16-byte boundaries
+    for (int idx = t13; idx < k2 * 16; idx += kStagers) {
+      const int k = idx >> 4, c = idx & 15;
+      const int cpy = (8 * c) / mpad, i0 = 8 * c - cpy * mpad;
+      uint4 w = make_uint4(0, 0, 0, 0);
+      if (k < m && cpy < group && i0 < m) {
+        const T* src = left + k * m + i0;
+        if (l_vec) {
+          w = *reinterpret_cast<const uint4*>(src);
+        } else {
+          uint32_t e[8];
 #pragma unroll
-      for (int e2 = 0; e2 < 4; ++e2) {
-        const int k0 = 8 * kc + 2 * e2;
-        const uint32_t lo = (row_ok && k0 < m) ? raw_l[k0 * m + i] : 0u;
-        const uint32_t hi = (row_ok && k0 + 1 < m) ? raw_l[(k0 + 1) * m + i] : 0u;
-        w[e2] = lo | (hi << 16);
+          for (int j = 0; j < 8; ++j) e[j] = i0 + j < m ? (uint32_t)reinterpret_cast<const uint16_t*>(src)[j] : 0u;
+          w = make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
+        }
       }
-      *reinterpret_cast<uint4*>(smem + kOffLL + (kc >> 3) * kAtomBytes + (r >> 3) * 1024 + (r & 7) * 128 + (((kc & 7) ^ (r & 7)) << 4)) =
-          make_uint4(w[0], w[1], w[2], w[3]);
+      *reinterpret_cast<uint4*>(smem + kOffLL + (c >> 3) * kAtomBytes + k * 128 + (((c & 7) ^ (k & 7)) << 4)) = w;
     }
     fence_proxy_async_smem();
     asm volatile("bar.sync 1, %0;" ::"n"(kStagers) : "memory");
@@ -189,9 +170,9 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc1 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 0, 0, 128, 128);
+      const uint32_t idesc1 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 0, 1, 128, 128);  // B = R as it lies in memory: N-major
       const uint64_t desc_x0 = umma_smem_desc_sw128(smem_base + kOffX, 16, 1024);
-      const uint64_t desc_r = umma_smem_desc_sw128(smem_base + kOffR, 16, 1024);
+      const uint64_t desc_r = umma_smem_desc_sw128(smem_base + kOffR, kAtomBytes, 1024);  // 64-column blocks one atom apart
       int sx = 0, phx = 0, s1 = 0, ph1 = 0;
       for (int it = 0; it < mine; ++it) {
         if (const int w = mbar_wait2(smem_u32(&misc->full_x[sx]), phx, smem_u32(&misc->d1_empty[s1]), ph1 ^ 1)) {
@@ -204,13 +185,13 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             const uint64_t off = (uint64_t)((ks >> 2) * (kAtomBytes >> 4) + (ks & 3) * 2);  // K atom, then 32 bytes per step
-            mma_f16_ss(tmem + s1 * 128, da + off, desc_r + off, idesc1, ks);
+            mma_f16_ss(tmem + s1 * 128, da + off, desc_r + (uint64_t)(ks * 128), idesc1, ks);  // 16 rows of R = 2048 bytes per step
           }
         } else {
 #pragma unroll 1
           for (int ks = 0; ks < (nc >> 4); ++ks) {
             const uint64_t off = (uint64_t)((ks >> 2) * (kAtomBytes >> 4) + (ks & 3) * 2);
-            mma_f16_ss(tmem + s1 * 128, da + off, desc_r + off, idesc1, ks);
+            mma_f16_ss(tmem + s1 * 128, da + off, desc_r + (uint64_t)(ks * 128), idesc1, ks);
           }
         }
         mma_commit(smem_u32(&misc->empty_x[sx]));
@@ -221,8 +202,8 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
     }
   } else if (warp == 2) {
     if (lane == 0) {
-      const uint32_t idesc2 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 0, 1, 128, group == 2 ? 256 : nc);
-      const uint64_t desc_ll = umma_smem_desc_sw128(smem_base + kOffLL, 16, 1024);
+      const uint32_t idesc2 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 1, 1, 128, group == 2 ? 256 : nc);  // A = LL, M-major
+      const uint64_t desc_ll = umma_smem_desc_sw128(smem_base + kOffLL, kAtomBytes, 1024);  // 64-row blocks one atom apart
       // N-major B operand: the stride between 64-column blocks along N is m rows (G = 2: token blocks interleave
       // with the column halves) or one atom (G = 1)
       const uint64_t desc_y0 = umma_smem_desc_sw128(smem_base + kOffY, group == 2 ? (uint32_t)(m * 128) : (uint32_t)kAtomBytes, 1024);
@@ -238,7 +219,7 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
         const uint64_t db0 = desc_y0 + (uint64_t)(sy * (kStageBytes >> 4));
 #pragma unroll 1
         for (int ks = 0; ks < ksteps2; ++ks) {
-          const uint64_t da2 = desc_ll + (uint64_t)((ks >> 2) * (kAtomBytes >> 4) + (ks & 3) * 2);
+          const uint64_t da2 = desc_ll + (uint64_t)(ks * 128);  // 16 rows of L = 2048 bytes per step
           mma_f16_ss(tmem + kColZ + e * 128, da2, db0 + (uint64_t)(ks * 128), idesc2, ks);  // 16 Y rows = 2048 bytes per step
         }
         mma_commit(smem_u32(&misc->y_empty[sy]));

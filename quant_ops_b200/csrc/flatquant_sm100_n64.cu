@@ -1,13 +1,15 @@
 // FlatQuant quantizer for sm_100a, right transform of size 64 (features = M x 64 with M = 16, 24, ... 64):
 // the activation-scale configuration (4096 = 64 x 64) runs here.  Right transforms of 16, 32 and 48 (1024 = 32 x 32,
-// 1536 = 32 x 48, 256 = 16 x 16) use the same layout: the TMA fills the missing columns of X with zeros, R^T is staged
-// with zero rows and columns, so the extra columns of Y and Z are exact zeros; they are not stored.
+// 1536 = 32 x 48, 256 = 16 x 16) use the same layout: the TMA fills the missing columns of X with zeros, R is staged
+// with zero columns, so the extra columns of Y and Z are exact zeros; they are not stored.
 //
 // One persistent CTA per SM works on groups of 2 tokens (2M <= 128 rows of 64 elements):
 //
 //   warp 0       TMA: 3-D tensor map (n, m, token), box 64 x M x 2 -> 2M rows of 128 bytes, 128-byte swizzle, 6 stages
-//   warp 1       issues Y = X . R        A = X rows (K-major), B = R^T (K-major), M = 128, N = 64, K = 64
-//   warp 2       issues Z = LL . Y2      A = LL = 2 copies of L^T, each starting on a 32-row boundary (K-major),
+//   warp 1       issues Y = X . R        A = X rows (K-major), B = R as it lies in memory (N-major), M = 128, N = 64,
+//                                        K = 64
+//   warp 2       issues Z = LL . Y2      A = LL = 2 copies of L^T, each starting on a 32-row boundary; staged as the
+//                                        rows of L laid along M (M-major), so neither transform is transposed;
 //                                        B = the 2 tokens' Y side by side along N (N-major, N = 128), K = M
 //   warps 3-10   Y pass: tensor memory -> round to the activation dtype -> shared memory in the B layout;
 //                warp (q, h) handles columns 32h..32h+31 of tensor-memory lanes 32q..32q+31
@@ -125,60 +127,30 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
   grid_launch_dependents();
 
   if (warp != 0) {
+    // Both transforms are staged as they lie in memory, 16 bytes at a time with the 128-byte XOR swizzle: the tensor
+    // core reads R as an N-major B operand (row k of R = one 128-byte row) and L as an M-major A operand (row k of L
+    // laid along M, once per token copy), so nothing is transposed here.
     constexpr int kStagers = kThreads - 32;
     const int t13 = tid - 32;
-    // raw copies of L and R into the (still unused) Y stages, all 16-byte loads in flight at once
-    uint16_t* raw_l = reinterpret_cast<uint16_t*>(smem + kOffY);
-    uint16_t* raw_r = reinterpret_cast<uint16_t*>(smem + kOffY + kStageBytes);
-    {
-      const int l_chunks = (m * m) / 8, r_chunks = nc * nc / 8;
-      constexpr int kMaxIter = (2 * 64 * 64 / 8 + kStagers - 1) / kStagers;
-      uint4 tmp[kMaxIter];
-#pragma unroll
-      for (int i = 0; i < kMaxIter; ++i) {
-        const int c = t13 + i * kStagers;
-        if (c < l_chunks) tmp[i] = reinterpret_cast<const uint4*>(left)[c];
-        else if (c - l_chunks < r_chunks) tmp[i] = reinterpret_cast<const uint4*>(right)[c - l_chunks];
-      }
-#pragma unroll
-      for (int i = 0; i < kMaxIter; ++i) {
-        const int c = t13 + i * kStagers;
-        if (c < l_chunks) reinterpret_cast<uint4*>(raw_l)[c] = tmp[i];
-        else if (c - l_chunks < r_chunks) reinterpret_cast<uint4*>(raw_r)[c - l_chunks] = tmp[i];
-      }
+    // R: rows k < nc, 8 pieces per row; columns past nc are zero (the first product always has N = 64)
+    for (int idx = t13; idx < nc * 8; idx += kStagers) {
+      const int k = idx >> 3, c = idx & 7;
+      uint4 w = make_uint4(0, 0, 0, 0);
+      if (8 * c < nc) w = *reinterpret_cast<const uint4*>(right + k * nc + 8 * c);
+      *reinterpret_cast<uint4*>(smem + kOffR + k * 128 + ((c ^ (k & 7)) << 4)) = w;
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(kStagers) : "memory");
-    // R^T, K-major: row = output column n; its 16-byte chunk jc holds R[8jc .. 8jc+7][n].  Lanes walk n, so the
-    // 2-byte reads of a warp are contiguous and each thread makes one 16-byte swizzled store.
-    for (int idx = t13; idx < 64 * 8; idx += kStagers) {
-      const int n = idx & 63, jc = idx >> 6;
-      uint32_t w[4] = {0, 0, 0, 0};  // rows and columns past N stay zero
-      if (n < nc && 8 * jc < nc) {
-#pragma unroll
-        for (int e2 = 0; e2 < 4; ++e2)
-          w[e2] = (uint32_t)raw_r[(8 * jc + 2 * e2) * nc + n] | ((uint32_t)raw_r[(8 * jc + 2 * e2 + 1) * nc + n] << 16);
-      }
-      *reinterpret_cast<uint4*>(smem + kOffR + (n >> 3) * 1024 + (n & 7) * 128 + ((jc ^ (n & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-    }
-    // LL, K-major: row (copy, i) = copy * mpad + i, column k holds L[k][i]; all other rows and the columns past m are zero
-    for (int idx = t13; idx < 128 * 8; idx += kStagers) {
-      const int r = idx & 127, kc = idx >> 7;
-      const int cpy = r / mpad, i = r - cpy * mpad;
-      const bool row_ok = cpy < kGroup && i < m;
-      uint32_t w[4];
-#pragma unroll
-      for (int e2 = 0; e2 < 4; ++e2) {
-        const int k0 = 8 * kc + 2 * e2;
-        const uint32_t lo = (row_ok && k0 < m) ? raw_l[k0 * m + i] : 0u;
-        const uint32_t hi = (row_ok && k0 + 1 < m) ? raw_l[(k0 + 1) * m + i] : 0u;
-        w[e2] = lo | (hi << 16);
-      }
-      *reinterpret_cast<uint4*>(smem + kOffLL + (r >> 3) * 1024 + (r & 7) * 128 + ((kc ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    // LL: rows k < k2 (rows m .. k2-1 pad the reduction length and must be zero), M position copy * mpad + i holds
+    // L[k][i]; every other M position of these rows is zero.  M is a multiple of 8: pieces are whole or empty.
+    for (int idx = t13; idx < k2 * 16; idx += kStagers) {
+      const int k = idx >> 4, c = idx & 15;
+      const int cpy = (8 * c) / mpad, i0 = 8 * c - cpy * mpad;
+      uint4 w = make_uint4(0, 0, 0, 0);
+      if (k < m && cpy < kGroup && i0 < m) w = *reinterpret_cast<const uint4*>(left + k * m + i0);
+      *reinterpret_cast<uint4*>(smem + kOffLL + (c >> 3) * (kAtomBytes / 2) + k * 128 + (((c & 7) ^ (k & 7)) << 4)) = w;
     }
     if (k2 != m) {
       // M is not a multiple of 16: rows m .. k2-1 of each token's Y block only pad the reduction; they are zeroed once
-      // (the Y pass never writes them) after everybody has finished reading the raw copies that live in the Y stages
-      asm volatile("bar.sync 1, %0;" ::"n"(kStagers) : "memory");
+      // (the Y pass never writes them)
       const int pad_rows = k2 - m, chunks = kYStages * kGroup * pad_rows * 8;
       for (int idx = t13; idx < chunks; idx += kStagers) {
         const int ch = idx & 7, pr = (idx >> 3) % pad_rows, blk = (idx >> 3) / pad_rows;  // blk = stage * kGroup + token
@@ -208,9 +180,9 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
     if (lane == 0) {
       // One thread feeds the tensor core, so its instruction count per MMA matters: descriptors are built once and
       // advanced with a single add on the address field (units of 16 bytes).
-      const uint32_t idesc1 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 0, 0, 128, 64);
+      const uint32_t idesc1 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 0, 1, 128, 64);  // B = R as it lies in memory: N-major
       const uint64_t desc_x0 = umma_smem_desc_sw128(smem_base + kOffX, 16, 1024);
-      const uint64_t desc_r = umma_smem_desc_sw128(smem_base + kOffR, 16, 1024);
+      const uint64_t desc_r = umma_smem_desc_sw128(smem_base + kOffR, 16, 1024);      // one 64-column block; 16 rows of R = 2048 bytes per step
       int sx = 0, phx = 0, s1 = 0, ph1 = 0;
       for (int it = 0; it < mine; ++it) {
         if (const int w = mbar_wait2(smem_u32(&misc->full_x[sx]), phx, smem_u32(&misc->d1_empty[s1]), ph1 ^ 1)) {
@@ -223,10 +195,10 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
         const uint64_t da = desc_x0 + (uint64_t)(sx * (kStageBytes >> 4));
         if (FULL) {  // four back-to-back issues without loop overhead
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) mma_f16_ss(tmem + s1 * 64, da + ks * 2, desc_r + ks * 2, idesc1, ks);
+          for (int ks = 0; ks < 4; ++ks) mma_f16_ss(tmem + s1 * 64, da + ks * 2, desc_r + ks * 128, idesc1, ks);
         } else {
 #pragma unroll 1
-          for (int ks = 0; ks < (nc >> 4); ++ks) mma_f16_ss(tmem + s1 * 64, da + ks * 2, desc_r + ks * 2, idesc1, ks);
+          for (int ks = 0; ks < (nc >> 4); ++ks) mma_f16_ss(tmem + s1 * 64, da + ks * 2, desc_r + ks * 128, idesc1, ks);
         }
         mma_commit(smem_u32(&misc->empty_x[sx]));
         mma_commit(smem_u32(&misc->d1_full[s1]));
@@ -238,8 +210,8 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
   } else if (warp == 2) {
     // second-product issuer: its waits and commits overlap with the first-product MMAs of later groups
     if (lane == 0) {
-      const uint32_t idesc2 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 0, 1, 128, 128);
-      const uint64_t desc_ll = umma_smem_desc_sw128(smem_base + kOffLL, 16, 1024);
+      const uint32_t idesc2 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 1, 1, 128, 128);  // A = LL, M-major
+      const uint64_t desc_ll = umma_smem_desc_sw128(smem_base + kOffLL, kAtomBytes / 2, 1024);  // two 64-row blocks of 64 k-rows
       const uint64_t desc_y0 = umma_smem_desc_sw128(smem_base + kOffY, (uint32_t)(k2 * 128), 1024);  // N blocks = tokens, k2 rows apart
       const int ksteps2 = k2 >> 4;
       int sy = 0, phy = 0;
@@ -254,7 +226,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
         TR(2, it, 1);
         uint64_t da2 = desc_ll, db2 = desc_y0 + (uint64_t)(sy * (kStageBytes >> 4));
 #pragma unroll 1
-        for (int ks = 0; ks < ksteps2; ++ks, da2 += 2, db2 += 128) mma_f16_ss(tmem + kColZ + e * 128, da2, db2, idesc2, ks);
+        for (int ks = 0; ks < ksteps2; ++ks, da2 += 128, db2 += 128) mma_f16_ss(tmem + kColZ + e * 128, da2, db2, idesc2, ks);
         mma_commit(smem_u32(&misc->y_empty[sy]));
         mma_commit(smem_u32(&misc->d2_full[e]));
         TR(2, it, 2);
