@@ -373,8 +373,9 @@ int qo_w4a4_linear_prepared(const void* x, int64_t ldx, const void* left, const 
   rc = qo_flatquant_quantize(x, ldx, left, right, a8, a_scale, tokens, m, n, clip_ratio, in_dtype, 0, QO_F32, stream);
   if (rc) return rc;
   t_gemm_path = 2;
+  // the prepared weights were not written by the quantizer just launched: the GEMM may request them before it waits
   return launch_gemm_sm100_s8(a8, reinterpret_cast<const int8_t*>(prepared), a_scale, w_scale, out, out_dtype, tokens, k, n_out,
-                              nullptr, bias, reinterpret_cast<cudaStream_t>(stream));
+                              nullptr, bias, reinterpret_cast<cudaStream_t>(stream), true);
 }
 
 int qo_pack_int4(const int8_t* codes, int32_t* packed, int64_t rows, int64_t features, void* stream) {

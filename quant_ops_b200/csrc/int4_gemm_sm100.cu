@@ -145,7 +145,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
                      const float* __restrict__ sa, const float* __restrict__ sb, OutT* __restrict__ out,
                      int32_t* __restrict__ acc_out, const OutT* __restrict__ bias, int t, int n, int k, int ksplit,
-                     uint32_t* __restrict__ status) {
+                     int b_early, uint32_t* __restrict__ status) {
   using C = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -175,6 +175,21 @@ gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_con
   const uint32_t tmem = bars->tmem_base;
   // Launched with programmatic stream serialization: the set-up above may overlap the tail of the preceding kernel
   // of the stream (the quantizer or the widening pass); nothing below reads or writes global memory before it is done.
+  // One exception, b_early: the caller says that B was not written by that kernel (weights prepared at load time,
+  // the predecessor is this call's quantizer, which releases its dependents only after its own dependency wait), so
+  // the B halves of the first stages are requested before the wait and their HBM latency overlaps it.
+  int early = 0;  // stages of the first work item whose B half is already on its way
+  if (b_early && warp == 0 && lane == 0 && blockIdx.x < ntiles) {
+    const int item = blockIdx.x, tile = item / ksplit, kz = item - tile * ksplit;
+    const int nb = tile % tiles_n;
+    const int ks0 = (int)((long long)kz * ksteps / ksplit), ks1 = (int)((long long)(kz + 1) * ksteps / ksplit);
+    early = min(C::kStages, ks1 - ks0);
+    for (int s = 0; s < early; ++s) {
+      const uint32_t bar = smem_u32(&bars->full[s]);
+      mbar_arrive_expect_tx(bar, C::kStageBytes);
+      tma_load_2d(smem_base + s * C::kStageBytes + kBM * kBK, &b_map, bar, 0, b_block_row(nb * BN, ks0 + s, ksteps));
+    }
+  }
   grid_dependency_wait();
 
   if (warp == 0) {
@@ -187,10 +202,14 @@ gemm_s8_sm100_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_con
         const int ks0 = (int)((long long)kz * ksteps / ksplit), ks1 = (int)((long long)(kz + 1) * ksteps / ksplit);
         for (int ks = ks0; ks < ks1; ++ks, ++step) {
           const int s = step % C::kStages, ph = (step / C::kStages) & 1;
-          if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1)) { atomicCAS(status, 0u, 0x500u + s); ok = false; break; }
           const uint32_t bar = smem_u32(&bars->full[s]);
-          mbar_arrive_expect_tx(bar, C::kStageBytes);
           const uint32_t dst = smem_base + s * C::kStageBytes;
+          if (step < early) {  // first use of the stage: nothing to wait for, the barrier already expects the bytes
+            tma_load_2d(dst, &a_map, bar, ks * kBK, mb * kBM);
+            continue;
+          }
+          if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1)) { atomicCAS(status, 0u, 0x500u + s); ok = false; break; }
+          mbar_arrive_expect_tx(bar, C::kStageBytes);
           tma_load_2d(dst, &a_map, bar, ks * kBK, mb * kBM);
           tma_load_2d(dst + kBM * kBK, &b_map, bar, 0, b_block_row(nb * BN, ks, ksteps));
         }
@@ -583,7 +602,8 @@ int make_map_b(CUtensorMap* map, const void* base, int64_t n, int64_t k, int box
 
 template <int BN, typename OutT>
 int launch_gemm_tile(const int8_t* a8, const int8_t* b8, const float* sa, const float* sb, void* out, int32_t* acc_out,
-                     const void* bias, int64_t t, int64_t k, int64_t n, uint32_t* status, cudaStream_t stream, int ksplit = 1) {
+                     const void* bias, int64_t t, int64_t k, int64_t n, uint32_t* status, cudaStream_t stream, int ksplit = 1,
+                     bool b_early = false) {
   using C = GemmCfg<BN>;
   CUtensorMap a_map, b_map;
   int rc = make_map_s8(&a_map, a8, t, k, kBM);
@@ -619,7 +639,7 @@ int launch_gemm_tile(const int8_t* a8, const int8_t* b8, const float* sa, const 
   }
   cfg.attrs = attr;
   QO_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, a_map, b_map, sa, sb, reinterpret_cast<OutT*>(out), acc_out,
-                                 reinterpret_cast<const OutT*>(bias), (int)t, (int)n, (int)k, ksplit, status));
+                                 reinterpret_cast<const OutT*>(bias), (int)t, (int)n, (int)k, ksplit, b_early ? 1 : 0, status));
   return check_launch("gemm_s8_sm100_kernel");
 }
 
@@ -696,7 +716,8 @@ int gemm_k_split(int dev, int64_t t, int64_t k, int64_t n) {
 
 template <typename OutT>
 int launch_gemm_typed(const int8_t* a8, const int8_t* b8, const float* sa, const float* sb, void* out, int32_t* acc_out,
-                      const void* bias, int64_t t, int64_t k, int64_t n, uint32_t* status, cudaStream_t stream) {
+                      const void* bias, int64_t t, int64_t k, int64_t n, uint32_t* status, cudaStream_t stream,
+                      bool b_early = false) {
   int dev = 0;
   QO_CUDA_TRY(cudaGetDevice(&dev));
   const int ksplit = gemm_k_split<256, OutT>(dev, t, k, n);
@@ -706,10 +727,10 @@ int launch_gemm_typed(const int8_t* a8, const int8_t* b8, const float* sa, const
     const int ksplit128 = gemm_k_split<128, OutT>(dev, t, k, n);
     const int64_t ctas128 = ((n + 127) / 128) * ksplit128;
     if (ksplit128 > 1 && ctas256 <= 74 && ctas128 > ctas256)
-      return launch_gemm_tile<128, OutT>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, ksplit128);
+      return launch_gemm_tile<128, OutT>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, ksplit128, b_early);
   }
   if (ksplit > 1)
-    return launch_gemm_tile<256, OutT>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, ksplit);
+    return launch_gemm_tile<256, OutT>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, ksplit, b_early);
   // enough 256 x 256 tiles for every SM: two accumulators per CTA share each B slice
   // (with few tiles and a short K the unshared tile does better: its epilogue overlaps the next main loop and its
   // smaller tiles fill the last wave more evenly)
@@ -719,10 +740,10 @@ int launch_gemm_typed(const int8_t* a8, const int8_t* b8, const float* sa, const
   // widest tile that does not leave most SMs idle
   const int64_t tiles_m = (t + kBM - 1) / kBM;
   if (n >= 256 && tiles_m * ((n + 255) / 256) >= 120)
-    return launch_gemm_tile<256, OutT>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream);
+    return launch_gemm_tile<256, OutT>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, 1, b_early);
   if (n >= 128 && tiles_m * ((n + 127) / 128) >= 100)
-    return launch_gemm_tile<128, OutT>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream);
-  return launch_gemm_tile<64, OutT>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream);
+    return launch_gemm_tile<128, OutT>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, 1, b_early);
+  return launch_gemm_tile<64, OutT>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, 1, b_early);
 }
 
 inline size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
@@ -751,7 +772,7 @@ bool gemm_sm100_supported(int64_t t, int64_t k, int64_t n, int64_t lda, int64_t 
 }
 
 int launch_gemm_sm100_s8(const int8_t* a8, const int8_t* b8, const float* sa, const float* sb, void* out, int out_dtype,
-                         int64_t t, int64_t k, int64_t n, int32_t* acc_out, const void* bias, cudaStream_t stream) {
+                         int64_t t, int64_t k, int64_t n, int32_t* acc_out, const void* bias, cudaStream_t stream, bool b_early) {
   if (reinterpret_cast<uintptr_t>(a8) % 16 || reinterpret_cast<uintptr_t>(b8) % 16 || reinterpret_cast<uintptr_t>(out) % 16 ||
       (acc_out && reinterpret_cast<uintptr_t>(acc_out) % 16) || (bias && reinterpret_cast<uintptr_t>(bias) % 4))
     return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: operands of the tcgen05 kernel must be 16-byte aligned");
@@ -759,8 +780,8 @@ int launch_gemm_sm100_s8(const int8_t* a8, const int8_t* b8, const float* sa, co
   QO_CUDA_TRY(cudaGetDevice(&dev));
   uint32_t* status = device_status_word(dev);
   if (!status) return fail(QO_ERR_CUDA, "int4_matmul: could not allocate the device status word");
-  if (out_dtype == QO_F16) return launch_gemm_typed<__half>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream);
-  return launch_gemm_typed<__nv_bfloat16>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream);
+  if (out_dtype == QO_F16) return launch_gemm_typed<__half>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, b_early);
+  return launch_gemm_typed<__nv_bfloat16>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, b_early);
 }
 
 // blocked: write the layout of the B operand (see the head of this file) instead of row-major

@@ -175,7 +175,8 @@ int launch_gemm_sm100(const int32_t* a, int64_t lda, const int32_t* b, int64_t b
 int launch_widen_rows(const int32_t* in, int64_t ld_words, int8_t* out, int64_t rows, int64_t k, cudaStream_t stream, bool blocked);
 size_t gemm_b8_bytes(int64_t n, int64_t k);  // bytes of the int8 B operand in the GEMM's blocked layout
 int launch_gemm_sm100_s8(const int8_t* a8, const int8_t* b8, const float* sa, const float* sb, void* out, int out_dtype,
-                         int64_t t, int64_t k, int64_t n, int32_t* acc_out, const void* bias, cudaStream_t stream);
+                         int64_t t, int64_t k, int64_t n, int32_t* acc_out, const void* bias, cudaStream_t stream,
+                         bool b_early = false);  // b_early: b8 was not written by the kernel that precedes the GEMM in the stream
 
 int launch_widen_b(const int32_t* b, int64_t bsk, int64_t bsn, int8_t* b8, int64_t n, int64_t k, cudaStream_t stream);
 int launch_gemm_sm100_s8_status(const int8_t* a8, const int8_t* b8, const float* sa, const float* sb, void* out,
