@@ -365,14 +365,16 @@ def run_other(args):
             tops = v / world * ops_per_token / 1e12
             return {"bound": "tensor", "achieved": tops, "peak": tc_peak, "unit": "TOP/s", "frac": tops / tc_peak, "traffic": None,
                     "peak_source": tc_src, "algorithmic_ops_per_token": ops_per_token}
-    elif args.workload == "quantize_wide":
-        tokens, m, n = 4096, 112, 128
+    elif args.workload in ("quantize_wide", "quantize_tokens"):
+        # quantize_tokens: the headline shape (64 x 64) at another token count, to separate the fixed cost of a
+        # launch (first-tile latency of the pipeline) from the streaming rate
+        tokens, m, n = (4096, 112, 128) if args.workload == "quantize_wide" else (int(args.tokens or 65536), 64, 64)
         feat = m * n
         x = torch.randn(tokens, feat, generator=g)
         x[:, torch.randperm(feat, generator=g)[: feat // 100]] *= 50
         left = torch.linalg.qr(torch.randn(m, m, dtype=torch.float64, generator=g)).Q.bfloat16().contiguous().to(dev)
         right = torch.linalg.qr(torch.randn(n, n, dtype=torch.float64, generator=g)).Q.bfloat16().contiguous().to(dev)
-        nsets = 3  # 3 x 147 MB > L2
+        nsets = max(2, int(400e6 // (tokens * feat * 2)) + 1)  # the input sets together exceed L2 (3 x 147 MB for quantize_wide)
         xs = [torch.roll(x, i, 0).bfloat16().to(dev) for i in range(nsets)]
         codes = [torch.empty(tokens, feat // 8, dtype=torch.int32, device=dev) for _ in range(nsets)]
         scales = [torch.empty(tokens, dtype=torch.float32, device=dev) for _ in range(nsets)]
@@ -383,8 +385,8 @@ def run_other(args):
             nat.check(lib.qo_flatquant_quantize(vp(xs[s]), feat, vp(left), vp(right), vp(codes[s]), vp(scales[s]), tokens, m, n,
                                                 CLIP, nat.QO_BF16, 1, nat.QO_F32, sp))
 
-        desc = {"workload": "flatquant_quantize x[4096,14336] bf16, 1% outlier channels x50, L 112x112 / R 128x128 orthogonal, clip 0.9, pack_int32",
-                "l2": "inputs rotate over 3 buffer sets (441 MB) > L2"}
+        desc = {"workload": f"flatquant_quantize x[{tokens},{feat}] bf16, 1% outlier channels x50, L {m}x{m} / R {n}x{n} orthogonal, clip 0.9, pack_int32",
+                "l2": f"inputs rotate over {nsets} buffer sets ({nsets * tokens * feat * 2 // 1000000} MB) > L2"}
         metric, unit, scale_value = "flatquant_quantize_GBps", "GB/s", lambda sec: algo / sec / 1e9
         roof = lambda v: {"bound": "hbm", "achieved": v, "peak": hbm_peak, "unit": "GB/s", "frac": v / hbm_peak, "traffic": None,
                           "peak_source": hbm_src, "algorithmic_bytes_per_launch": algo}
@@ -393,7 +395,7 @@ def run_other(args):
         if args.workload == "gemm":
             t, k, n_out = 4096, 4096, 4096
         else:
-            t, k, n_out = int(args.tokens), 14336, 4096
+            t, k, n_out = int(args.tokens or 16), 14336, 4096
         nw = max(2, int(200e6 // (n_out * k // 2)) + 1)  # weight buffers that together exceed L2
         wps = [torch.randint(-2**31, 2**31 - 1, (n_out, k // 8), generator=g, dtype=torch.int32).to(dev) for _ in range(nw)]
         sw = (torch.rand(n_out, generator=g) * 0.01 + 0.001).to(dev)
@@ -495,8 +497,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="quantize", choices=["quantize", "quantize_wide", "gemm", "linear", "stack"])
-    ap.add_argument("--tokens", type=int, default=16, help="rows of the `linear` workload")
+    ap.add_argument("--workload", default="quantize", choices=["quantize", "quantize_wide", "quantize_tokens", "gemm", "linear", "stack"])
+    ap.add_argument("--tokens", type=int, default=None, help="rows of the `linear` (default 16) and `quantize_tokens` (default 65536) workloads")
     ap.add_argument("--prepared", action="store_true", help="`linear`: weights also kept widened to int8 (qo_prepare_weights)")
     args = ap.parse_args()
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
