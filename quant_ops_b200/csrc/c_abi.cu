@@ -298,7 +298,8 @@ int qo_w4a4_linear(const void* x, int64_t ldx, const void* left, const void* rig
     int8_t* b8 = reinterpret_cast<int8_t*>(ws + o_b);
     rc = qo_flatquant_quantize(x, ldx, left, right, a8, a_scale8, tokens, m, n, clip_ratio, in_dtype, 0, QO_F32, stream);
     if (rc) return rc;
-    if ((rc = launch_widen_rows(w_packed, k / 8, b8, n_out, k, reinterpret_cast<cudaStream_t>(stream), true))) return rc;
+    // the weights are widened beside the quantizer just launched: it neither reads the packed weights nor writes b8
+    if ((rc = launch_widen_rows(w_packed, k / 8, b8, n_out, k, reinterpret_cast<cudaStream_t>(stream), true, true))) return rc;
     t_gemm_path = 2;
     return launch_gemm_sm100_s8(a8, b8, a_scale8, w_scale, out, out_dtype, tokens, k, n_out, nullptr, bias,
                                 reinterpret_cast<cudaStream_t>(stream));

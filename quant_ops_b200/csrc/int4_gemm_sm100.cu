@@ -63,8 +63,12 @@ struct WidenJob {
   int64_t ld_words, rows, kquads;  // kquads = K / 32 = groups of four packed words per row
   int64_t ksteps;                  // 0: row-major output, else the blocked layout
 };
+// chained: the kernel was launched with programmatic stream serialization behind a kernel whose output it does not
+// touch (the fused layer: the activation quantizer, while this pass widens the weights), so it runs beside that
+// kernel; before it ends it waits for that kernel, so that whoever waits for this one has waited for both.
 __global__ void __launch_bounds__(256)
-widen_rows2_kernel(WidenJob j0, WidenJob j1) {
+widen_rows2_kernel(WidenJob j0, WidenJob j1, int chained) {
+  grid_launch_dependents();  // the GEMM that follows may set itself up; it waits before it reads anything
   const int64_t n0 = j0.rows * j0.kquads, total = n0 + j1.rows * j1.kquads;
   for (int64_t i = blockIdx.x * 256LL + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
     const bool second = i >= n0;
@@ -77,6 +81,7 @@ widen_rows2_kernel(WidenJob j0, WidenJob j1) {
     o[0] = make_uint4(a.x, a.y, b.x, b.y);
     o[1] = make_uint4(c.x, c.y, d.x, d.y);
   }
+  if (chained) grid_dependency_wait();
 }
 
 // reference B layout [K/8, N] with N contiguous: transpose 32 x 32 words through shared memory so that the reads run
@@ -785,7 +790,10 @@ int launch_gemm_sm100_s8(const int8_t* a8, const int8_t* b8, const float* sa, co
 }
 
 // blocked: write the layout of the B operand (see the head of this file) instead of row-major
-int launch_widen_rows(const int32_t* in, int64_t ld_words, int8_t* out, int64_t rows, int64_t k, cudaStream_t stream, bool blocked) {
+// beside_previous: neither `in` nor `out` is touched by the kernel that precedes this one in the stream, and that
+// kernel releases its dependents only after its own dependency wait (the quantizers do): the pass may run beside it
+int launch_widen_rows(const int32_t* in, int64_t ld_words, int8_t* out, int64_t rows, int64_t k, cudaStream_t stream, bool blocked,
+                      bool beside_previous) {
   const int64_t ksteps = blocked ? (k + kBK - 1) / kBK : 0;
   if ((k % 32) == 0 && (ld_words % 4) == 0 && reinterpret_cast<uintptr_t>(in) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) {
     const WidenJob job = {reinterpret_cast<const uint32_t*>(in), reinterpret_cast<uint8_t*>(out), ld_words, rows, k / 32, ksteps};
@@ -793,7 +801,20 @@ int launch_widen_rows(const int32_t* in, int64_t ld_words, int8_t* out, int64_t 
     int64_t blocks = (rows * (k / 32) + 255) / 256;
     if (blocks > 148 * 32) blocks = 148 * 32;
     if (blocks < 1) blocks = 1;
-    widen_rows2_kernel<<<(int)blocks, 256, 0, stream>>>(job, none);
+    if (beside_previous) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3((unsigned)blocks);
+      cfg.blockDim = dim3(256);
+      cfg.stream = stream;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      QO_CUDA_TRY(cudaLaunchKernelEx(&cfg, widen_rows2_kernel, job, none, 1));
+    } else {
+      widen_rows2_kernel<<<(int)blocks, 256, 0, stream>>>(job, none, 0);
+    }
     return check_launch("widen_rows2_kernel");
   }
   const int64_t total = rows * (k / 8);
@@ -820,14 +841,14 @@ int launch_gemm_sm100(const int32_t* a, int64_t lda, const int32_t* b, int64_t b
     const int64_t total = (t + n) * (k / 32);
     int64_t blocks = (total + 255) / 256;
     if (blocks > 148 * 32) blocks = 148 * 32;
-    widen_rows2_kernel<<<(int)blocks, 256, 0, stream>>>(ja, jb);
+    widen_rows2_kernel<<<(int)blocks, 256, 0, stream>>>(ja, jb, 0);
     if ((rc = check_launch("widen_rows2_kernel"))) return rc;
     return launch_gemm_sm100_s8(a8, b8, sa, sb, out, out_dtype, t, k, n, acc_out, bias, stream);
   }
-  rc = launch_widen_rows(a, lda, a8, t, k, stream, false);
+  rc = launch_widen_rows(a, lda, a8, t, k, stream, false, false);
   if (rc) return rc;
   if (bsk == 1) {
-    rc = launch_widen_rows(b, bsn, b8, n, k, stream, true);  // rows of the weight matrix [Nout, K/8]
+    rc = launch_widen_rows(b, bsn, b8, n, k, stream, true, false);  // rows of the weight matrix [Nout, K/8]
   } else {
     dim3 grid((unsigned)((n + 31) / 32), (unsigned)((k / 8 + 31) / 32));
     widen_transpose_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const uint32_t*>(b), bsk, bsn,
@@ -840,7 +861,7 @@ int launch_gemm_sm100(const int32_t* a, int64_t lda, const int32_t* b, int64_t b
 
 // ---- pieces for callers that bring their own scratch and status word (int4_gemm_static.cu) ------------------------
 int launch_widen_b(const int32_t* b, int64_t bsk, int64_t bsn, int8_t* b8, int64_t n, int64_t k, cudaStream_t stream) {
-  if (bsk == 1) return launch_widen_rows(b, bsn, b8, n, k, stream, true);
+  if (bsk == 1) return launch_widen_rows(b, bsn, b8, n, k, stream, true, false);
   dim3 grid((unsigned)((n + 31) / 32), (unsigned)((k / 8 + 31) / 32));
   widen_transpose_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const uint32_t*>(b), bsk, bsn,
                                                    reinterpret_cast<uint8_t*>(b8), n, k / 8, (k + kBK - 1) / kBK);

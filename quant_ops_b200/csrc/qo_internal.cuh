@@ -172,7 +172,8 @@ int launch_gemm_sm100(const int32_t* a, int64_t lda, const int32_t* b, int64_t b
                       cudaStream_t stream);
 
 // pieces of the tcgen05 GEMM, used separately by the fused layer
-int launch_widen_rows(const int32_t* in, int64_t ld_words, int8_t* out, int64_t rows, int64_t k, cudaStream_t stream, bool blocked);
+int launch_widen_rows(const int32_t* in, int64_t ld_words, int8_t* out, int64_t rows, int64_t k, cudaStream_t stream, bool blocked,
+                      bool beside_previous = false);  // beside_previous: may run beside the kernel before it (see int4_gemm_sm100.cu)
 size_t gemm_b8_bytes(int64_t n, int64_t k);  // bytes of the int8 B operand in the GEMM's blocked layout
 int launch_gemm_sm100_s8(const int8_t* a8, const int8_t* b8, const float* sa, const float* sb, void* out, int out_dtype,
                          int64_t t, int64_t k, int64_t n, int32_t* acc_out, const void* bias, cudaStream_t stream,
