@@ -11,11 +11,13 @@
 //      B8 with TMA (128-byte swizzle) through a ring of shared-memory stages, warp 1 issues tcgen05.mma kind::i8
 //      (int8 x int8 -> int32) into tensor memory, warps 2-5 read the accumulators back, apply
 //      (float(acc) * scale_a[row]) * scale_b[col] and store fp16 / bf16.  Two accumulator stages in tensor memory
-//      let the epilogue of one tile overlap the main loop of the next.
+//      let the epilogue of one tile overlap the main loop of the next.  Short activation matrices split K over the
+//      2, 4 or 8 CTAs of a thread-block cluster, which add their partial sums through distributed shared memory.
 //
 // Arithmetic is that of the reference kernel (src/quant_ops/ops/quantization/int4_matmul/kernels/
 // cuda_int4_matmul_kernel.cu:104-116): exact int32 accumulation, then the two float32 multiplies in that order.
-// Every mbarrier wait is bounded; a wait that runs out records a code in the device status word.
+// Every mbarrier wait is bounded; a wait that runs out records a code in the device status word.  The cluster barriers
+// of the K-split are hardware barriers that every thread reaches on every path (no thread returns early).
 #include <mutex>
 
 #include "qo_internal.cuh"
