@@ -93,11 +93,21 @@ QO_API int qo_flatquant_transform(const void* x, int64_t ldx, const void* left, 
                                   int64_t tokens, int m, int n, int in_dtype, void* stream);
 
 /*
- * Synchronises `stream` and reports whether any kernel of this library gave up on a bounded device-side wait
- * since the last call (QO_ERR_DEVICE_TIMEOUT, and the flag is cleared) -- the reference's counterpart is the
- * cudaGetLastError check after its per-call synchronise, cuda_quant_kernel.cu:380-387.
+ * Synchronises `stream` and reports whether any kernel of this library (qo_int4_matmul_static included) gave up on
+ * a bounded device-side wait since the last call (QO_ERR_DEVICE_TIMEOUT, and the flag is cleared) -- the
+ * reference's counterpart is the cudaGetLastError check after its per-call synchronise, cuda_quant_kernel.cu:380-387.
+ * Allocates nothing.
  */
 QO_API int qo_device_status(void* stream);
+
+/*
+ * Exercises the failure path on purpose, harmlessly: one warp waits (limit 1024 polls, well under a millisecond) on
+ * a barrier that nothing arrives on, records a site code in the device status word and returns.  The next
+ * qo_device_status() then reports QO_ERR_DEVICE_TIMEOUT once, and the device stays fully usable.  No trap, no
+ * fault.  It has no counterpart in the reference, whose only check is cudaGetLastError after a blocking synchronise
+ * (cuda_quant_kernel.cu:380-387); it exists so that a host can test its own handling of a timed-out kernel.
+ */
+QO_API int qo_selftest_wait_timeout(void* stream);
 
 /*
  * int4 codes (int8 or packed) times per-token scale -> float32 [tokens, features].
@@ -126,7 +136,9 @@ QO_API size_t qo_int4_matmul_workspace_bytes(int64_t tokens, int64_t k, int64_t 
  *   out        [tokens, n_out] contiguous, QO_F16 (the reference's output type) or QO_BF16
  *   acc_out    optional int32 [tokens, n_out]: raw accumulators, for bit-exact checks (NULL to skip)
  *   workspace  device scratch of at least qo_int4_matmul_workspace_bytes(); NULL lets the library use a
- *              per-device buffer it allocates (and keeps) itself
+ *              per-device buffer it allocates (and keeps) itself.  That buffer is shared by every NULL-workspace
+ *              call on the device: issue such calls on one stream at a time.  Callers with several streams or
+ *              threads pass their own workspace per call (the torch binding does).
  */
 QO_API int qo_int4_matmul(const int32_t* a, int64_t lda, const int32_t* b, int64_t b_stride_k,
                           int64_t b_stride_n, const float* scale_a, const float* scale_b, void* out,

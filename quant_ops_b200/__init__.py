@@ -10,7 +10,7 @@ from __future__ import annotations
 
 from . import _native
 from .decompose import get_decompose_dim
-from .ops import (dequantize_int4, flatquant_cuda, flatquant_dynamic_quantize, int4_matmul, int4_matmul_cuda,
+from .ops import (dequantize_int4, device_status, flatquant_cuda, flatquant_dynamic_quantize, int4_matmul, int4_matmul_cuda,
                   int4_matmul_ex, pack_int4_to_int32, prepare_weights, quantize_weights_int4, unpack_int32_to_int4, w4a4_linear,
                   w4a4_linear_prepared)
 from . import meta as _meta  # noqa: F401  (registers the fake kernels)
@@ -31,5 +31,5 @@ CUDA_AVAILABLE = _cuda_available()
 __all__ = [
     "flatquant_dynamic_quantize", "flatquant_cuda", "dequantize_int4", "int4_matmul", "int4_matmul_cuda",
     "int4_matmul_ex", "w4a4_linear", "w4a4_linear_prepared", "prepare_weights", "get_decompose_dim", "pack_int4_to_int32", "unpack_int32_to_int4",
-    "quantize_weights_int4", "W4A4Linear", "sharding", "CUDA_AVAILABLE", "__version__",
+    "quantize_weights_int4", "device_status", "W4A4Linear", "sharding", "CUDA_AVAILABLE", "__version__",
 ]

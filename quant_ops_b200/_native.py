@@ -28,6 +28,7 @@ PROTOTYPES = {
     "qo_flatquant_quantize": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _i64, _int, _int, _f32, _int, _int, _int, _vp]),
     "qo_flatquant_transform": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _int, _int, _int, _vp]),
     "qo_device_status": (_int, [_vp]),
+    "qo_selftest_wait_timeout": (_int, [_vp]),
     "qo_dequantize_int4": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _int, _vp]),
     "qo_int4_matmul_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "qo_int4_matmul": (_int, [_vp, _i64, _vp, _i64, _i64, _vp, _vp, _vp, _int, _i64, _i64, _i64, _vp, _vp, _sz, _vp]),

@@ -1,6 +1,7 @@
 // extern "C" entry points: argument validation, kernel selection, workspaces.  No kernels live here.
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "qo_internal.cuh"
 
@@ -46,11 +47,17 @@ int require_device(int* dev_out) {
   return QO_OK;
 }
 
-// Grow-only per-device scratch the library owns when the caller passes no workspace.
+// Grow-only per-device scratch the library owns when the caller passes no workspace.  ONE buffer per device, shared
+// by every call that passes no workspace: such calls must be issued on one stream at a time (calls on different
+// streams would overwrite each other's operands).  A buffer that has become too small is not freed when a larger
+// one replaces it -- kernels already enqueued may still use it -- but kept until qo_release_workspaces(), so growing
+// neither synchronises the device nor frees memory under a running kernel.
 struct Scratch {
   std::mutex mu;
   void* ptr[kMaxDevices] = {};
   size_t bytes[kMaxDevices] = {};
+  struct Retired { int dev; void* ptr; };
+  std::vector<Retired> retired;
 };
 Scratch g_scratch;       // GEMM / fused layer
 Scratch g_host_staging;  // device side of the host-buffer quantizer
@@ -58,14 +65,11 @@ Scratch g_host_staging;  // device side of the host-buffer quantizer
 int scratch_get(Scratch& s, int dev, size_t need, void** out) {
   std::lock_guard<std::mutex> lock(s.mu);
   if (s.bytes[dev] < need) {
-    if (s.ptr[dev]) {
-      QO_CUDA_TRY(cudaDeviceSynchronize());
-      QO_CUDA_TRY(cudaFree(s.ptr[dev]));
-      s.ptr[dev] = nullptr;
-      s.bytes[dev] = 0;
-    }
-    size_t grow = need + need / 4;
-    QO_CUDA_TRY(cudaMalloc(&s.ptr[dev], grow));
+    const size_t grow = need + need / 4;
+    void* fresh = nullptr;
+    QO_CUDA_TRY(cudaMalloc(&fresh, grow));
+    if (s.ptr[dev]) s.retired.push_back({dev, s.ptr[dev]});
+    s.ptr[dev] = fresh;
     s.bytes[dev] = grow;
   }
   *out = s.ptr[dev];
@@ -190,12 +194,17 @@ int qo_device_status(void* stream) {
   int dev = 0, rc = require_device(&dev);
   if (rc) return rc;
   QO_CUDA_TRY(cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream)));
-  uint32_t* word = device_status_word(dev);
-  if (!word) return QO_OK;
-  uint32_t code = 0;
-  QO_CUDA_TRY(cudaMemcpy(&code, word, sizeof code, cudaMemcpyDeviceToHost));
+  // two words can carry a report: the one the regular entry points share (it exists once any of them has launched a
+  // tcgen05 kernel on this device) and the one inside the library that qo_int4_matmul_static uses.  Reading them
+  // allocates nothing, so a host that may not allocate can call this too.
+  uint32_t code = 0, code_static = 0;
+  if (uint32_t* word = device_status_word_if_any(dev)) {
+    QO_CUDA_TRY(cudaMemcpy(&code, word, sizeof code, cudaMemcpyDeviceToHost));
+    if (code != 0) QO_CUDA_TRY(cudaMemset(word, 0, sizeof code));
+  }
+  if ((rc = static_status_take(dev, &code_static))) return rc;
+  if (code == 0) code = code_static;
   if (code == 0) return QO_OK;
-  QO_CUDA_TRY(cudaMemset(word, 0, sizeof code));
   return fail(QO_ERR_DEVICE_TIMEOUT, "a kernel gave up waiting (site 0x%x); its outputs are not valid", code);
 }
 
@@ -277,8 +286,10 @@ int qo_w4a4_linear(const void* x, int64_t ldx, const void* left, const void* rig
   if (n_out < 0) return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear: negative n_out");
   const int64_t k = (int64_t)m * n;
   if (m <= 0 || n <= 0 || k % 8) return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear: m*n must be a positive multiple of 8");
+  if (out_dtype != QO_F16 && out_dtype != QO_BF16) return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear: out_dtype must be QO_F16 or QO_BF16");
+  if (tokens < 0) return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear: negative token count");
   if (tokens == 0 || n_out == 0) return QO_OK;
-  if (!w_packed || !w_scale || !out) return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear: null pointer argument");
+  if (!x || !left || !right || !w_packed || !w_scale || !out) return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear: null pointer argument");
   int dev = 0, rc = require_device(&dev);
   if (rc) return rc;
   const size_t need = qo_w4a4_linear_workspace_bytes(tokens, k, n_out);
@@ -351,7 +362,7 @@ int qo_w4a4_linear_prepared(const void* x, int64_t ldx, const void* left, const 
   const int64_t k = (int64_t)m * n;
   if (m <= 0 || n <= 0 || k % 8) return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear: m*n must be a positive multiple of 8");
   if (tokens == 0 || n_out == 0) return QO_OK;
-  if (!w_packed || !prepared || !w_scale || !out) return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear: null pointer argument");
+  if (!x || !left || !right || !w_packed || !prepared || !w_scale || !out) return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear: null pointer argument");
   if (out_dtype != QO_F16 && out_dtype != QO_BF16) return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear: out_dtype must be QO_F16 or QO_BF16");
   int dev = 0, rc = require_device(&dev);
   if (rc) return rc;
@@ -486,13 +497,17 @@ int qo_release_workspaces(void) {
     std::lock_guard<std::mutex> lock(s->mu);
     for (int d = 0; d < kMaxDevices; ++d) {
       if (!s->ptr[d]) continue;
-      if (cudaSetDevice(d) == cudaSuccess) {
-        cudaDeviceSynchronize();
-        if (cudaFree(s->ptr[d]) != cudaSuccess) rc = fail(QO_ERR_CUDA, "cudaFree of a library workspace failed");
-      }
+      s->retired.push_back({d, s->ptr[d]});
       s->ptr[d] = nullptr;
       s->bytes[d] = 0;
     }
+    for (const Scratch::Retired& r : s->retired) {
+      if (cudaSetDevice(r.dev) == cudaSuccess) {
+        cudaDeviceSynchronize();
+        if (cudaFree(r.ptr) != cudaSuccess) rc = fail(QO_ERR_CUDA, "cudaFree of a library workspace failed");
+      }
+    }
+    s->retired.clear();
   }
   cudaSetDevice(cur);
   return rc;

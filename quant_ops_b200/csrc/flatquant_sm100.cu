@@ -24,7 +24,6 @@
 // the float32 product is off by less than 2^-22.
 //
 // Every wait on an mbarrier is bounded; a wait that runs out stores a code in the status word and the CTA leaves.
-#include <cstdlib>
 #include <mutex>
 
 #include "flatquant_sm100_common.cuh"
@@ -74,8 +73,7 @@ template <typename T, int NDIM, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 flatquant_sm100_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restrict__ left,
                        const T* __restrict__ right, void* __restrict__ out, void* __restrict__ scales,
-                       long long tokens, int m, float clip, int scale_dtype, uint32_t flags,
-                       uint32_t* __restrict__ status) {
+                       long long tokens, int m, float clip, int scale_dtype, uint32_t* __restrict__ status) {
   using C = Cfg<NDIM>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -218,8 +216,8 @@ flatquant_sm100_kernel(const __grid_constant__ CUtensorMap x_map, const T* __res
     if (lane == 0) {
       const uint32_t idesc1 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 0, 0, 128, NDIM);
       const uint32_t idesc2 = umma_idesc(1, Fmt<T>::id, Fmt<T>::id, 0, 1, 128, NDIM);
-      const uint32_t y_lbo = (flags & 1u) ? 1024u : (uint32_t)kAtomBytes;
-      const uint32_t y_sbo = (flags & 1u) ? (uint32_t)kAtomBytes : 1024u;
+      // Y as an N-major B operand: 64-column blocks one atom apart (leading offset), 8-row k groups 1024 bytes apart
+      constexpr uint32_t y_lbo = (uint32_t)kAtomBytes, y_sbo = 1024u;
       long long my_tiles = 0;
       if ((long long)blockIdx.x < ntiles) my_tiles = (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
       bool ok = true;
@@ -448,9 +446,12 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
+std::mutex g_status_mu;
+uint32_t* g_status_words[64] = {};
+
 uint32_t* status_word(int dev) {
-  static std::mutex mu;
-  static uint32_t* words[64] = {};
+  std::mutex& mu = g_status_mu;
+  uint32_t** words = g_status_words;
   std::lock_guard<std::mutex> lock(mu);
   if (dev < 0 || dev >= 64) return nullptr;
   if (!words[dev]) {
@@ -476,12 +477,8 @@ int launch_one(const CUtensorMap& map, const void* left, const void* right, void
   const int g = 128 / m;
   const int64_t ntiles = (tokens + g - 1) / g;
   const int grid = (int)(ntiles < sms ? ntiles : sms);
-  static const uint32_t flags = [] {
-    const char* e = std::getenv("QO_DEBUG_FLAGS");
-    return e ? (uint32_t)std::strtoul(e, nullptr, 0) : 0u;
-  }();
   kern<<<grid, kThreads, C::kSmemBytes, stream>>>(map, reinterpret_cast<const T*>(left), reinterpret_cast<const T*>(right),
-                                                  out, scales, (long long)tokens, m, clip, scale_dtype, flags, status);
+                                                  out, scales, (long long)tokens, m, clip, scale_dtype, status);
   return check_launch("flatquant_sm100_kernel");
 }
 
@@ -498,6 +495,11 @@ int launch_mode(int mode, const CUtensorMap& map, const void* left, const void* 
 }  // namespace
 
 uint32_t* device_status_word(int dev) { return status_word(dev); }
+uint32_t* device_status_word_if_any(int dev) {
+  if (dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(g_status_mu);
+  return g_status_words[dev];
+}
 
 bool flatquant_sm100_supported(int64_t ldx, int m, int n, int in_dtype, const void* x, const void* left, const void* right,
                                float clip) {

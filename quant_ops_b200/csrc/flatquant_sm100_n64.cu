@@ -35,14 +35,6 @@ namespace {
 using namespace ptx;
 using namespace fq;
 
-// Pipeline tracing for development builds (-DQO_TRACE): CTA 0 records clock64() at role hand-offs.
-#ifdef QO_TRACE
-__device__ long long* g_trace = nullptr;
-#define TR(role, it, ev) do { if (g_trace && blockIdx.x == 0 && (it) < 16) g_trace[((role) * 16 + (it)) * 8 + (ev)] = clock64(); } while (0)
-#else
-#define TR(role, it, ev) do { } while (0)
-#endif
-
 constexpr int kThreads = 864;                  // 27 warps: TMA, two MMA issuers, 8 (Y pass) + 2 x 8 (quantize pass)
 constexpr int kEpi1Warp0 = 3, kEpi2Warp0 = 11; // first warp of the Y pass / of the two quantize sets
 constexpr int kGroup = 2;                      // tokens per group
@@ -169,7 +161,6 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       long long grp = blockIdx.x;
       for (int it = 0; it < mine; ++it, grp += gridDim.x) {
         if (!mbar_wait(smem_u32(&misc->empty_x[s]), ph ^ 1)) { atomicCAS(status, 0u, 0x600u + s); break; }
-        TR(0, it, 0);
         const uint32_t bar = smem_u32(&misc->full_x[s]);
         mbar_arrive_expect_tx(bar, bytes);
         tma_load_3d(smem_base + kOffX + s * kStageBytes, &x_map, bar, 0, 0, (int)(grp * kGroup));
@@ -189,9 +180,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
           atomicCAS(status, 0u, 0x600u + 0x10u * w + sx);
           break;
         }
-        TR(1, it, 0);
         tc_fence_after();
-        TR(1, it, 1);
         const uint64_t da = desc_x0 + (uint64_t)(sx * (kStageBytes >> 4));
         if (FULL) {  // four back-to-back issues without loop overhead
 #pragma unroll
@@ -202,7 +191,6 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
         }
         mma_commit(smem_u32(&misc->empty_x[sx]));
         mma_commit(smem_u32(&misc->d1_full[s1]));
-        TR(1, it, 2);
         if (++sx == kXStages) { sx = 0; phx ^= 1; }
         if (++s1 == kYStages) { s1 = 0; ph1 ^= 1; }
       }
@@ -221,15 +209,12 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
           atomicCAS(status, 0u, 0x620u + 0x10u * w + sy);
           break;
         }
-        TR(2, it, 0);
         tc_fence_after();
-        TR(2, it, 1);
         uint64_t da2 = desc_ll, db2 = desc_y0 + (uint64_t)(sy * (kStageBytes >> 4));
 #pragma unroll 1
         for (int ks = 0; ks < ksteps2; ++ks, da2 += 128, db2 += 128) mma_f16_ss(tmem + kColZ + e * 128, da2, db2, idesc2, ks);
         mma_commit(smem_u32(&misc->y_empty[sy]));
         mma_commit(smem_u32(&misc->d2_full[e]));
-        TR(2, it, 2);
         if (++sy == kYStages) { sy = 0; phy ^= 1; }
       }
     }
@@ -243,13 +228,11 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
         break;
       }
       tc_fence_after();
-      if (tid == kEpi1Warp0 * 32) TR(3, it, 0);
       uint32_t v[32];
       tmem_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + s * 64 + h * 32, v);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive_warp(smem_u32(&misc->d1_empty[s]));  // accumulators are in registers: the stage can be overwritten
-      if (tid == kEpi1Warp0 * 32) TR(3, it, 1);
       if (r < rows_group) {
         const int yr = r < m ? r : r - m + k2;  // row of the Y stage: token c's rows start at c * k2
         uint8_t* yrow = smem + kOffY + s * kStageBytes + yr * 128;
@@ -265,7 +248,6 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       }
       fence_proxy_async_smem();
       mbar_arrive_warp(smem_u32(&misc->y_full[s]));
-      if (tid == kEpi1Warp0 * 32) TR(3, it, 2);
       if (++s == kYStages) { s = 0; ph ^= 1; }
     }
   } else {
@@ -283,7 +265,6 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       const int ph = use & 1, buf = use % 3;
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&misc->d2_full[e]), ph))) { atomicCAS(status, 0u, 0x800u + e); break; }
       tc_fence_after();
-      if (lane == 0 && q == 2 && h == 0) TR(4 + e, use, 0);
       const long long tok = grp * kGroup + c;
       const bool valid = active && tok < tokens;
       const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + kColZ + e * 128 + (active ? c : 0) * 64;
@@ -292,7 +273,6 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive_warp(smem_u32(&misc->d2_empty[e]));  // the Z accumulators of this stage are free again
-      if (lane == 0 && q == 2 && h == 0) TR(4 + e, use, 1);
 
       // round Z to the activation dtype once, as packed pairs; both passes work on the pairs
       uint32_t zz[16];
@@ -320,7 +300,6 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
         const uint32_t gs = smem_u32(&misc->set_sync[e]);
         mbar_arrive_warp(gs);
         if (!__all_sync(0xffffffffu, mbar_wait(gs, ph))) { atomicCAS(status, 0u, 0x810u + e); break; }
-        if (lane == 0 && q == 2 && h == 0) TR(4 + e, use, 2);
         {
           // the slot buffer of this use is next written three uses later, after two more passes of this barrier
           const float4 p4 = *reinterpret_cast<const float4*>(&misc->absmax_part[e][buf][c < kGroup ? c : 0][0]);
@@ -338,7 +317,6 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
         clamp_needed = __any_sync(0xffffffffu, !(row_amax * inv_s < 7.4f));
       }
       const bool zero_scale = (MODE != kTransform) && (s == 0.f);
-      if (lane == 0 && q == 2 && h == 0) TR(4 + e, use, 3);
 
       {
         const int c0 = h * 32;
@@ -391,7 +369,6 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
           }
         }
       }
-      if (lane == 0 && q == 2 && h == 0) TR(4 + e, use, 4);
     }
   }
 
@@ -450,12 +427,6 @@ int launch_mode(int mode, const CUtensorMap& map, const void* left, const void* 
 }
 
 }  // namespace
-
-#ifdef QO_TRACE
-extern "C" __attribute__((visibility("default"))) int qo_debug_set_trace(long long* p) {
-  return (int)cudaMemcpyToSymbol(g_trace, &p, sizeof p);
-}
-#endif
 
 bool flatquant_sm100_n64_supported(int m, int n) { return n >= 16 && n <= 64 && (n % 16) == 0 && m >= 16 && m <= 64 && (m % 8) == 0; }
 

@@ -31,6 +31,9 @@ namespace {
 constexpr int kSlices = 8;       // warps per 16 output channels: each takes a contiguous eighth of K
 constexpr int kChunkWords = 16;  // packed words of one weight row per chunk (4 lanes x 16 bytes)
 constexpr int kBatch = 4;        // chunks per batch of weight loads (two batches in flight)
+constexpr size_t kSmemOptIn = 227 * 1024;  // shared memory one CTA may use on sm_100 (static + dynamic)
+// bytes of the partial-sum exchange, a static array of the kernel below
+constexpr size_t red_bytes(int nt, int rt) { return (size_t)kSlices * rt * nt * 16 * 9 * sizeof(int); }
 
 template <typename OutT>
 __device__ __forceinline__ OutT to_out(float v);
@@ -201,10 +204,11 @@ int launch_cfg(const uint32_t* a, int64_t lda, const uint32_t* b, int64_t ldb, c
   if (smem > 0) {
     int dev = 0;
     QO_CUDA_TRY(cudaGetDevice(&dev));
-    static size_t configured[64] = {};
-    if (configured[dev & 63] < smem) {
-      QO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-      configured[dev & 63] = 200 * 1024;
+    static bool configured[64] = {};
+    if (!configured[dev & 63]) {
+      // static and dynamic shared memory together must stay within the opt-in limit
+      QO_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kSmemOptIn - red_bytes(NT, RT))));
+      configured[dev & 63] = true;
     }
   }
   const unsigned grid = (unsigned)((n + 16 * RT - 1) / (16 * RT));
@@ -229,7 +233,7 @@ int launch_nt(const uint32_t* a, int64_t lda, const uint32_t* b, int64_t ldb, co
   const size_t stage = (size_t)tokens * ((size_t)nchunks * 64 + 64);
   if (stage <= 92 * 1024)  // two CTAs of 16 channels per SM
     return launch_cfg<NT, 1, true, OutT>(a, lda, b, ldb, sa, sb, out, acc_out, bias, tokens, nchunks, n, stage, weights_first, stream);
-  if (stage <= 200 * 1024)  // one CTA of 32 channels per SM shares the copy
+  if (stage + red_bytes(NT, 2) <= kSmemOptIn)  // one CTA of 32 channels per SM shares the copy
     return launch_cfg<NT, 2, true, OutT>(a, lda, b, ldb, sa, sb, out, acc_out, bias, tokens, nchunks, n, stage, weights_first, stream);
   return launch_cfg<NT, 1, false, OutT>(a, lda, b, ldb, sa, sb, out, acc_out, bias, tokens, nchunks, n, 0, weights_first, stream);
 }

@@ -788,7 +788,8 @@ int launch_gemm_sm100_s8(const int8_t* a8, const int8_t* b8, const float* sa, co
   uint32_t* status = device_status_word(dev);
   if (!status) return fail(QO_ERR_CUDA, "int4_matmul: could not allocate the device status word");
   if (out_dtype == QO_F16) return launch_gemm_typed<__half>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, b_early);
-  return launch_gemm_typed<__nv_bfloat16>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, b_early);
+  if (out_dtype == QO_BF16) return launch_gemm_typed<__nv_bfloat16>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, b_early);
+  return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: out_dtype must be QO_F16 or QO_BF16");
 }
 
 // blocked: write the layout of the B operand (see the head of this file) instead of row-major
@@ -877,7 +878,8 @@ int launch_gemm_sm100_s8_status(const int8_t* a8, const int8_t* b8, const float*
       (acc_out && reinterpret_cast<uintptr_t>(acc_out) % 16))
     return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: operands of the tcgen05 kernel must be 16-byte aligned");
   if (out_dtype == QO_F16) return launch_gemm_typed<__half>(a8, b8, sa, sb, out, acc_out, nullptr, t, k, n, status, stream);
-  return launch_gemm_typed<__nv_bfloat16>(a8, b8, sa, sb, out, acc_out, nullptr, t, k, n, status, stream);
+  if (out_dtype == QO_BF16) return launch_gemm_typed<__nv_bfloat16>(a8, b8, sa, sb, out, acc_out, nullptr, t, k, n, status, stream);
+  return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: out_dtype must be QO_F16 or QO_BF16");
 }
 
 }  // namespace qo

@@ -27,10 +27,21 @@ struct DeviceAddresses {
   uint32_t* status = nullptr;
 };
 
+std::mutex g_addr_mu;
+DeviceAddresses g_addr_table[64];
+
+// the addresses of device `dev` if a call already resolved them
+bool static_addresses_if_resolved(int dev, DeviceAddresses* out) {
+  std::lock_guard<std::mutex> lock(g_addr_mu);
+  if (!g_addr_table[dev].scratch) return false;
+  *out = g_addr_table[dev];
+  return true;
+}
+
 // Device addresses of the two arrays on the current device (index `dev`), resolved on first use.
 int static_addresses(int dev, DeviceAddresses* out) {
-  static std::mutex mu;
-  static DeviceAddresses table[64];
+  std::mutex& mu = g_addr_mu;
+  DeviceAddresses* table = g_addr_table;
   if (dev < 0 || dev >= 64) return fail(QO_ERR_NO_DEVICE, "int4_matmul_static: device index %d out of range", dev);
   std::lock_guard<std::mutex> lock(mu);
   if (!table[dev].scratch) {
@@ -56,6 +67,28 @@ int static_addresses(int dev, DeviceAddresses* out) {
 inline size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 
 }  // namespace
+
+// Reads and clears the status word of qo_int4_matmul_static on device `dev` (which must be current and idle on the
+// caller's stream).  Plain cudaMemcpy from / to the resolved symbol address: nothing is allocated.  *code stays 0 when
+// the entry point has not been used on this device yet.
+int static_status_take(int dev, uint32_t* code) {
+  *code = 0;
+  if (dev < 0 || dev >= 64) return QO_OK;
+  uint32_t* word = nullptr;
+  {
+    // only a device on which the entry point already ran has anything to report; do not resolve the symbol here
+    DeviceAddresses probe;
+    if (static_addresses_if_resolved(dev, &probe)) word = probe.status;
+  }
+  if (!word) return QO_OK;
+  QO_CUDA_TRY(cudaMemcpy(code, word, sizeof *code, cudaMemcpyDeviceToHost));
+  if (*code != 0) {
+    const uint32_t zero = 0;
+    QO_CUDA_TRY(cudaMemcpy(word, &zero, sizeof zero, cudaMemcpyHostToDevice));
+  }
+  return QO_OK;
+}
+
 }  // namespace qo
 
 using namespace qo;

@@ -148,6 +148,10 @@ int launch_transform_generic(const void* x, int64_t ldx, const void* left, const
                              int m, int n, int in_dtype, cudaStream_t stream);
 // device word that kernels set when a bounded wait runs out (nullptr if it could not be allocated)
 uint32_t* device_status_word(int dev);
+// the same word if some launch on `dev` already created it, else nullptr (never allocates)
+uint32_t* device_status_word_if_any(int dev);
+// status word of qo_int4_matmul_static (a device array inside the library): read and clear, allocation-free
+int static_status_take(int dev, uint32_t* code);
 
 int launch_dequantize(const void* codes, const void* scales, float* out, int64_t tokens, int64_t features,
                       int packed, int scale_dtype, cudaStream_t stream);

@@ -37,9 +37,13 @@ at::Tensor row_major(const at::Tensor& t) {
   return t.contiguous();
 }
 
-std::tuple<at::Tensor, at::Tensor> flatquant_dynamic_quantize(const at::Tensor& input, const at::Tensor& left_trans,
-                                                              const at::Tensor& right_trans, double clip_ratio,
-                                                              bool pack_int32) {
+// scale_dtype: dtype of the returned per-token scales; float32 (what the reference's CUDA op returns) when absent
+std::tuple<at::Tensor, at::Tensor> flatquant_dynamic_quantize_ex(const at::Tensor& input, const at::Tensor& left_trans,
+                                                                 const at::Tensor& right_trans, double clip_ratio,
+                                                                 bool pack_int32,
+                                                                 c10::optional<at::ScalarType> scale_dtype_opt) {
+  const at::ScalarType scale_dtype = scale_dtype_opt.has_value() ? *scale_dtype_opt : at::kFloat;
+  const int sdt = to_qo_dtype(scale_dtype, "scale_dtype");
   TORCH_CHECK(input.is_cuda() && left_trans.is_cuda() && right_trans.is_cuda(),
               "flatquant_dynamic_quantize: all tensors must be CUDA tensors");
   TORCH_CHECK(left_trans.dim() == 2 && left_trans.size(0) == left_trans.size(1), "left_trans must be square [M, M]");
@@ -60,12 +64,18 @@ std::tuple<at::Tensor, at::Tensor> flatquant_dynamic_quantize(const at::Tensor& 
   const int64_t tokens = x2.size(0);
   at::Tensor codes = pack_int32 ? at::empty({tokens, features / 8}, input.options().dtype(at::kInt))
                                 : at::empty({tokens, features}, input.options().dtype(at::kChar));
-  at::Tensor scales = at::empty({tokens}, input.options().dtype(at::kFloat));
+  at::Tensor scales = at::empty({tokens}, input.options().dtype(scale_dtype));
   check_status(qo_flatquant_quantize(x2.data_ptr(), tokens > 1 ? x2.stride(0) : features, left.data_ptr(),
                                      right.data_ptr(), codes.data_ptr(), scales.data_ptr(), tokens, (int)m, (int)n,
-                                     (float)clip_ratio, dt, pack_int32 ? 1 : 0, QO_F32, current_stream()),
+                                     (float)clip_ratio, dt, pack_int32 ? 1 : 0, sdt, current_stream()),
                "flatquant_dynamic_quantize");
   return {codes, scales};
+}
+
+std::tuple<at::Tensor, at::Tensor> flatquant_dynamic_quantize(const at::Tensor& input, const at::Tensor& left_trans,
+                                                              const at::Tensor& right_trans, double clip_ratio,
+                                                              bool pack_int32) {
+  return flatquant_dynamic_quantize_ex(input, left_trans, right_trans, clip_ratio, pack_int32, c10::nullopt);
 }
 
 std::tuple<at::Tensor, at::Tensor> int4_matmul_ex(const at::Tensor& a, const at::Tensor& b, const at::Tensor& scale_a,
@@ -252,6 +262,7 @@ std::tuple<at::Tensor, at::Tensor> quantize_weights_int4(const at::Tensor& w) {
 
 TORCH_LIBRARY(quant_ops, m) {
   m.def("flatquant_dynamic_quantize(Tensor input, Tensor left_trans, Tensor right_trans, float clip_ratio=1, bool pack_int32=False) -> (Tensor, Tensor)");
+  m.def("flatquant_dynamic_quantize_ex(Tensor input, Tensor left_trans, Tensor right_trans, float clip_ratio=1, bool pack_int32=False, ScalarType? scale_dtype=None) -> (Tensor, Tensor)");
   m.def("int4_matmul(Tensor a, Tensor b, Tensor scale_a, Tensor scale_b) -> Tensor");
   m.def("int4_matmul_ex(Tensor a, Tensor b, Tensor scale_a, Tensor scale_b, ScalarType out_dtype, bool return_acc=False) -> (Tensor, Tensor)");
   m.def("dequantize_int4(Tensor quantized, Tensor scales, bool packed_int32=False) -> Tensor");
@@ -265,6 +276,7 @@ TORCH_LIBRARY(quant_ops, m) {
 
 TORCH_LIBRARY_IMPL(quant_ops, CUDA, m) {
   m.impl("flatquant_dynamic_quantize", &flatquant_dynamic_quantize);
+  m.impl("flatquant_dynamic_quantize_ex", &flatquant_dynamic_quantize_ex);
   m.impl("int4_matmul", &int4_matmul);
   m.impl("int4_matmul_ex", &int4_matmul_ex);
   m.impl("dequantize_int4", &dequantize_int4);

@@ -35,6 +35,12 @@ def _flatquant_fake(input, left_trans, right_trans, clip_ratio=1.0, pack_int32=F
     return out, input.new_empty((tokens,), dtype=torch.float32)
 
 
+@register_fake("quant_ops::flatquant_dynamic_quantize_ex")
+def _flatquant_ex_fake(input, left_trans, right_trans, clip_ratio=1.0, pack_int32=False, scale_dtype=None):
+    out, _ = _flatquant_fake(input, left_trans, right_trans, clip_ratio, pack_int32)
+    return out, input.new_empty((input.size(0),), dtype=scale_dtype or torch.float32)
+
+
 @register_fake("quant_ops::dequantize_int4")
 def _dequant_fake(quantized, scales, packed_int32=False):
     feats = quantized.size(1) * (8 if packed_int32 else 1)

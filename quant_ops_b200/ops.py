@@ -19,9 +19,31 @@ _ops = torch.ops.quant_ops
 
 
 def flatquant_dynamic_quantize(input_tensor: torch.Tensor, left_trans: torch.Tensor, right_trans: torch.Tensor,
-                               clip_ratio: float = 1.0, pack_int32: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Kronecker transform L^T.X.R per token, clip-scaled absmax scale, int4 codes (int8 or 8 per int32)."""
-    return _ops.flatquant_dynamic_quantize(input_tensor, left_trans, right_trans, float(clip_ratio), bool(pack_int32))
+                               clip_ratio: float = 1.0, pack_int32: bool = False, *,
+                               scale_dtype: Optional[torch.dtype] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Kronecker transform L^T.X.R per token, clip-scaled absmax scale, int4 codes (int8 or 8 per int32).
+
+    The positional arguments are the reference's.  `scale_dtype` (keyword only, an addition) stores the per-token
+    scales as float16 / bfloat16 instead of float32; the value is the same, the reference's scale being a value of
+    the input dtype already (float16 scales of bfloat16 inputs are rounded once more).
+    """
+    if scale_dtype is None:
+        return _ops.flatquant_dynamic_quantize(input_tensor, left_trans, right_trans, float(clip_ratio), bool(pack_int32))
+    return _ops.flatquant_dynamic_quantize_ex(input_tensor, left_trans, right_trans, float(clip_ratio), bool(pack_int32), scale_dtype)
+
+
+def device_status(stream: Optional[torch.cuda.Stream] = None) -> None:
+    """Waits for `stream` (default: the current stream) and raises RuntimeError if a kernel of this library gave up
+    on one of its bounded device-side waits since the last check; outputs written since then are not valid.
+
+    The reference checks cudaGetLastError after a blocking synchronise inside every call
+    (src/quant_ops/ops/quantization/flatquant/kernels/cuda_quant_kernel.cu:380-387); here calls never block, so the
+    check is a call of its own, to be made wherever the caller synchronises anyway.
+    """
+    import ctypes
+
+    st = stream if stream is not None else torch.cuda.current_stream()
+    _native.check(_native.lib.qo_device_status(ctypes.c_void_p(st.cuda_stream)))
 
 
 def flatquant_cuda(input_tensor, left_trans, right_trans, clip_ratio: float = 1.0, pack_int32: bool = False):

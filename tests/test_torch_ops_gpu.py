@@ -130,3 +130,70 @@ def test_layer_against_the_float_simulation():
     sim = O.fake_quant_linear(t2f(x), t2f(left), t2f(right), 0.9, wq, sw, "bf16")
     bound = 2e-2 * np.abs(sim).max(axis=1, keepdims=True)
     assert np.all(np.abs(y - sim) <= bound), float((np.abs(y - sim) / bound).max())
+
+
+def _layer_inputs(tokens, k, n_out, seed):
+    x, left, right = make_inputs(tokens, k, "bf16", seed, True)
+    w = torch.randn(n_out, k, generator=torch.Generator().manual_seed(seed + 1)) * 0.02
+    wp, sw = q.quantize_weights_int4(w.to(DEV))
+    return x.to(DEV), left.to(DEV), right.to(DEV), wp, sw
+
+
+@pytest.mark.parametrize("tokens", [8, 200])
+def test_gemm_and_fused_layer_in_a_cuda_graph(tokens):
+    """int4_matmul and w4a4_linear (both GEMM kernels: weight-streaming and tensor-core) captured and replayed on new
+    data: launches go to the capturing stream, nothing synchronises, the workspace comes from the graph's pool."""
+    xd, ld, rd, wp, sw = _layer_inputs(tokens, 4096, 512, 100 + tokens)
+    codes, scales = q.flatquant_dynamic_quantize(xd, ld, rd, 0.9, True)
+    ref_mm = q.int4_matmul(codes, wp.t(), scales, sw)
+    ref_lin = q.w4a4_linear(xd, ld, rd, wp, sw, None, 0.9, torch.bfloat16)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        g_codes, g_scales = q.flatquant_dynamic_quantize(xd, ld, rd, 0.9, True)
+        g_mm = q.int4_matmul(g_codes, wp.t(), g_scales, sw)
+        g_lin = q.w4a4_linear(xd, ld, rd, wp, sw, None, 0.9, torch.bfloat16)
+    xd.copy_(torch.roll(xd, 3, 0))
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(g_mm, torch.roll(ref_mm, 3, 0)) and torch.equal(g_lin, torch.roll(ref_lin, 3, 0))
+    q.device_status()
+
+
+@pytest.mark.parametrize("backend", ["aot_eager", "inductor"])
+def test_ops_trace_under_torch_compile(backend):
+    """quantize -> int4_matmul and the W4A4Linear module compiled as one graph (fullgraph=True: a graph break would
+    raise): the dispatcher ops and their fake kernels carry the trace, as the reference's registration intends
+    (src/quant_ops/ops/quantization/flatquant/kernels/cuda_quant_kernel.cu:393-417, src/quant_ops/meta_ops.py:22-37)."""
+    xd, ld, rd, wp, sw = _layer_inputs(96, 4096, 256, 7)
+
+    def chain(x, left, right, w, s):
+        codes, scales = q.flatquant_dynamic_quantize(x, left, right, 0.9, True)
+        return q.int4_matmul(codes, w.t(), scales, s), q.dequantize_int4(codes, scales, True)
+
+    want_out, want_deq = chain(xd, ld, rd, wp, sw)
+    got_out, got_deq = torch.compile(chain, fullgraph=True, backend=backend)(xd, ld, rd, wp, sw)
+    assert torch.equal(got_out, want_out) and torch.equal(got_deq, want_deq)
+
+    layer = q.W4A4Linear(4096, 256, clip_ratio=0.9, dtype=torch.bfloat16, device=DEV)
+    layer.weight_packed.copy_(wp)
+    layer.weight_scale.copy_(sw)
+    layer.left_trans.copy_(ld)
+    layer.right_trans.copy_(rd)
+    want = layer(xd.view(8, 12, 4096))
+    got = torch.compile(layer, fullgraph=True, backend=backend)(xd.view(8, 12, 4096))
+    assert got.shape == (8, 12, 256) and torch.equal(got, want)
+    q.device_status()
+
+
+def test_scale_dtype_keyword_and_device_status():
+    """The 2-byte scale store is reachable from Python; the values are the float32 scales (bf16 inputs give bf16 values)."""
+    x, left, right = make_inputs(40, 4096, "bf16", 12, True)
+    xd, ld, rd = x.to(DEV), left.to(DEV), right.to(DEV)
+    c32, s32 = q.flatquant_dynamic_quantize(xd, ld, rd, 0.9, True)
+    cb, sb = q.flatquant_dynamic_quantize(xd, ld, rd, 0.9, True, scale_dtype=torch.bfloat16)
+    assert sb.dtype == torch.bfloat16 and torch.equal(cb, c32) and torch.equal(sb.float(), s32)
+    ch, sh = q.flatquant_dynamic_quantize(xd, ld, rd, 0.9, True, scale_dtype=torch.float16)
+    assert sh.dtype == torch.float16 and torch.equal(ch, c32) and torch.equal(sh, s32.half())
+    assert torch.equal(q.dequantize_int4(cb, sb, True), q.dequantize_int4(c32, s32, True))
+    q.device_status()

@@ -48,7 +48,30 @@ def test_two_calls_in_a_row_match_the_regular_entry_point():
             assert torch.equal(got, want)
             got2 = static_matmul(ap, b, sa, sb, "fp16")
             assert torch.equal(got2, want)
+    # qo_device_status also reads (and would clear) the status word that lives inside the library next to the scratch
+    assert lib.qo_device_status(stream_ptr()) == N.QO_OK, lib.qo_last_error()
+
+
+def test_the_call_allocates_no_device_memory():
+    """Free device memory, as the driver reports it, is the same before and after a call (and after the status
+    check): the scratch is part of the loaded library, nothing is allocated or freed per call."""
+    ap, wp, sa, sb = problem(200, 2048, 1024, 21)
+    out = torch.empty((200, 1024), dtype=torch.float16, device=DEV)
+
+    def call():
+        N.check(lib.qo_int4_matmul_static(ptr(ap), ap.stride(0), ptr(wp), 1, wp.stride(0), ptr(sa), ptr(sb), ptr(out),
+                                          N.QO_F16, 200, 2048, 1024, stream_ptr()))
+        torch.cuda.synchronize()
+
+    call()  # the first call on a device resolves the addresses of the library's arrays (and loads the kernels)
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        call()
     assert lib.qo_device_status(stream_ptr()) == N.QO_OK
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, f"free device memory changed by {free0 - free1} bytes across allocation-free calls"
+    want = abi_int4_matmul(ap, wp.t(), sa, sb, "fp16", policy=2)
+    assert torch.equal(out, want)
 
 
 def test_limits_are_reported_not_exceeded():
