@@ -28,15 +28,22 @@ def shard_sizes(total: int, world: int) -> List[int]:
     return [shard_rows(total, world, r)[1] for r in range(world)]
 
 
-def all_gather_rows(local: torch.Tensor, total_rows: int, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
-    """Concatenates the ranks' row slices ([rows_r, cols], slice sizes from shard_rows) into [total_rows, cols]."""
+def all_gather_rows(local: torch.Tensor, total_rows: int, group: Optional[dist.ProcessGroup] = None,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Concatenates the ranks' row slices ([rows_r, cols], slice sizes from shard_rows) into [total_rows, cols].
+
+    `out`, if given, receives the result (a caller that gathers every step keeps one buffer instead of allocating;
+    it also lets the collective run on a side stream without the allocator's cross-stream bookkeeping)."""
     world = dist.get_world_size(group)
     sizes = shard_sizes(total_rows, world)
     if local.shape[0] != sizes[dist.get_rank(group)]:
         raise ValueError(f"this rank holds {local.shape[0]} rows, its shard of {total_rows} has {sizes[dist.get_rank(group)]}")
     tail = tuple(local.shape[1:])
+    if out is not None and (tuple(out.shape) != (total_rows,) + tail or out.dtype != local.dtype or not out.is_contiguous()):
+        raise ValueError("out must be a contiguous [total_rows, cols] tensor of the local slice's dtype")
     if len(set(sizes)) == 1:
-        out = local.new_empty((total_rows,) + tail)
+        if out is None:
+            out = local.new_empty((total_rows,) + tail)
         dist.all_gather_into_tensor(out, local.contiguous(), group=group)
         return out
     # uneven split (sizes differ by at most one row): pad every slice to the largest, gather, drop the padding
@@ -45,7 +52,11 @@ def all_gather_rows(local: torch.Tensor, total_rows: int, group: Optional[dist.P
     padded[: local.shape[0]] = local
     gathered = local.new_empty((world * widest,) + tail)
     dist.all_gather_into_tensor(gathered, padded, group=group)
-    return torch.cat([gathered[r * widest: r * widest + sizes[r]] for r in range(world)], dim=0)
+    pieces = [gathered[r * widest: r * widest + sizes[r]] for r in range(world)]
+    if out is None:
+        return torch.cat(pieces, dim=0)
+    torch.cat(pieces, dim=0, out=out)
+    return out
 
 
 def sharded_apply(fn: Callable[[torch.Tensor], torch.Tensor], x_full_rows: int, x_local: torch.Tensor,

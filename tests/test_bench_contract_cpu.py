@@ -25,6 +25,15 @@ def test_reference_arm_prints_one_json_line_with_the_contract_keys():
     cb = d["cpu_baseline"]
     assert cb["kind"] == "port" and cb["cores"] >= 1 and cb["value"] == d["value"] and cb["sample"]
     assert d["e2e"] == {"value": d["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert "all 8192 tokens" in cb["sample"]                      # the same workload as the GPU arm, not a slice of it
+    assert d["gemm"][0]["value"] > 0 and d["stack"]["unit"] == "tokens/s"  # the other parts of the metric, on the CPU
+
+
+def test_reference_arm_honours_the_workload_switch():
+    r = run("--impl", "reference", "--workload", "gemm", "--steps", "1", "--warmup", "0")
+    assert r.returncode == 0, r.stderr[-2000:]
+    d = json.loads([ln for ln in r.stdout.splitlines() if ln.startswith("{")][0])
+    assert d["metric"] == "int4_matmul_TOPs" and d["unit"] == "TOP/s" and d["impl"] == "reference" and d["value"] > 0
 
 
 def test_product_arm_fails_loudly_without_a_gpu():

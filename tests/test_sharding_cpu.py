@@ -40,6 +40,10 @@ def _worker(rank, world, port, total, fail_rank):
         assert torch.equal(local, row_fn(full)[start:start + count])
         gathered = sharding.sharded_apply(row_fn, total, full[start:start + count], gather=True)
         assert torch.equal(gathered, row_fn(full))
+        keep = torch.empty(total, 3)
+        assert sharding.all_gather_rows(local, total, out=keep) is keep and torch.equal(keep, row_fn(full))
+        with pytest.raises(ValueError):
+            sharding.all_gather_rows(local, total, out=torch.empty(total + 1, 3))
         if rank == fail_rank:  # a rank holding the wrong number of rows is reported on the host, before any collective
             with pytest.raises(ValueError):
                 sharding.all_gather_rows(torch.zeros(count + 1, 3), total)
