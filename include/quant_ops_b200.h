@@ -244,7 +244,8 @@ QO_API int qo_last_gemm_path(void);
 /*
  * Kernel selection for the calling thread: 0 = automatic (tcgen05 kernel when the shape has one, else the
  * generic SIMT kernel), 1 = generic SIMT kernels only, 2 = tcgen05 kernels only (QO_ERR_UNSUPPORTED when the
- * shape has none).  Both kinds compute the same results; the switch exists so that tests can check each.
+ * shape has none), 3 = as 2 but without the CTA-pair GEMM kernel (large products then run on the single-CTA
+ * tcgen05 kernels).  All kinds compute the same results; the switch exists so that tests can check each.
  */
 QO_API int qo_set_kernel_policy(int policy);
 /* Free the per-device buffers the library allocated itself. */

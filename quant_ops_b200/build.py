@@ -19,7 +19,7 @@ CSRC = os.path.join(PKG, "csrc")
 OBJ = os.path.join(PKG, "build")
 LIB = os.path.join(PKG, "libquant_ops_b200.so")
 CU_SOURCES = ["c_abi.cu", "flatquant_generic.cu", "flatquant_sm100.cu", "flatquant_sm100_n64.cu", "flatquant_sm100_n128.cu", "elementwise.cu", "int4_gemm_generic.cu",
-              "int4_gemm_sm100.cu", "int4_gemm_static.cu", "int4_gemm_skinny.cu", "selftest.cu"]
+              "int4_gemm_sm100.cu", "int4_gemm_sm100_pair.cu", "int4_gemm_sm100_unpack.cu", "int4_gemm_static.cu", "int4_gemm_skinny.cu", "selftest.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
               "-Xcompiler", "-fPIC,-fvisibility=hidden,-O3", "-Xptxas", "-v"]
 

@@ -20,6 +20,7 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 void clear_error() { t_error[0] = 0; }
+int current_kernel_policy() { return t_policy; }
 
 namespace {
 
@@ -121,7 +122,7 @@ int qo_last_quantizer_path(void) { return t_quant_path; }
 int qo_last_gemm_path(void) { return t_gemm_path; }
 
 int qo_set_kernel_policy(int policy) {
-  if (policy < 0 || policy > 2) return fail(QO_ERR_INVALID_ARGUMENT, "kernel policy must be 0, 1 or 2");
+  if (policy < 0 || policy > 3) return fail(QO_ERR_INVALID_ARGUMENT, "kernel policy must be 0, 1, 2 or 3");
   t_policy = policy;
   return QO_OK;
 }
@@ -158,7 +159,7 @@ int qo_flatquant_quantize(const void* x, int64_t ldx, const void* left, const vo
   if ((rc = require_device(nullptr))) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const bool fast_ok = flatquant_sm100_supported(ldx, m, n, in_dtype, x, left, right, clip_ratio);
-  if (t_policy == 2 && !fast_ok)
+  if (t_policy >= 2 && !fast_ok)
     return fail(QO_ERR_UNSUPPORTED, "flatquant: no tcgen05 kernel for m=%d n=%d dtype=%d ldx=%lld", m, n, in_dtype, (long long)ldx);
   if (fast_ok && t_policy != 1) {
     t_quant_path = 2;
@@ -179,7 +180,7 @@ int qo_flatquant_transform(const void* x, int64_t ldx, const void* left, const v
   if ((rc = require_device(nullptr))) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const bool fast_ok = flatquant_sm100_supported(ldx, m, n, in_dtype, x, left, right, 1.0f);
-  if (t_policy == 2 && !fast_ok)
+  if (t_policy >= 2 && !fast_ok)
     return fail(QO_ERR_UNSUPPORTED, "flatquant_transform: no tcgen05 kernel for m=%d n=%d dtype=%d", m, n, in_dtype);
   if (fast_ok && t_policy != 1) {
     t_quant_path = 2;
@@ -247,7 +248,7 @@ static int int4_matmul_impl(const int32_t* a, int64_t lda, const int32_t* b, int
     return launch_gemm_skinny(a, lda, b, bsn, sa, sb, out, out_dtype, t, k, n, acc_out, bias, st, b_is_layer_weight);
   }
   const bool fast_ok = k > 0 && gemm_sm100_supported(t, k, n, lda, bsk, bsn);
-  if (t_policy == 2 && !fast_ok)
+  if (t_policy >= 2 && !fast_ok)
     return fail(QO_ERR_UNSUPPORTED, "int4_matmul: no tcgen05 kernel for t=%lld k=%lld n=%lld", (long long)t, (long long)k, (long long)n);
   if (fast_ok && t_policy != 1) {
     const size_t need = gemm_sm100_workspace_bytes(t, k, n);
@@ -299,9 +300,13 @@ int qo_w4a4_linear(const void* x, int64_t ldx, const void* left, const void* rig
   }
   if (workspace_bytes < need) return fail(QO_ERR_WORKSPACE, "w4a4_linear: workspace of %zu bytes, need %zu", workspace_bytes, need);
   char* ws = reinterpret_cast<char*>(workspace);
-  if (t_policy != 1 && tokens > 32 && gemm_sm100_supported(tokens, k, n_out, k / 8, 1, k / 8)) {
-    // tensor-core route: the quantizer writes int8 codes, which is the GEMM's A operand as it is; only the weights
-    // are widened.  Layout: int8 codes [tokens, k] | scales | int8 weights (blocked).
+  // prefill sizes: the quantizer packs, and the GEMM that unpacks in the kernel takes the packed codes and the packed
+  // weights as they are (the packed route below); otherwise ...
+  const bool unpack_route = t_policy != 1 && gemm_unpack_preferred(tokens, k, n_out) &&
+                            gemm_unpack_supported(tokens, k, n_out, workspace, k / 8, w_packed, 1, k / 8);
+  if (!unpack_route && t_policy != 1 && tokens > 32 && gemm_sm100_supported(tokens, k, n_out, k / 8, 1, k / 8)) {
+    // ... tensor-core route with int8 operands: the quantizer writes int8 codes, which is that GEMM's A operand as it
+    // is; only the weights are widened.  Layout: int8 codes [tokens, k] | scales | int8 weights (blocked).
     int8_t* a8 = reinterpret_cast<int8_t*>(ws);
     const size_t o_scale = align_up((size_t)tokens * (size_t)k, 256);
     float* a_scale8 = reinterpret_cast<float*>(ws + o_scale);

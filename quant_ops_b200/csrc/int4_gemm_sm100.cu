@@ -19,6 +19,7 @@
 // Every mbarrier wait is bounded; a wait that runs out records a code in the device status word.  The cluster barriers
 // of the K-split are hardware barriers that every thread reaches on every path (no thread returns early).
 #include <mutex>
+#include <type_traits>
 
 #include "qo_internal.cuh"
 #include "sm100_ptx.cuh"
@@ -738,6 +739,17 @@ int launch_gemm_typed(const int8_t* a8, const int8_t* b8, const float* sa, const
   }
   if (ksplit > 1)
     return launch_gemm_tile<256, OutT>(a8, b8, sa, sb, out, acc_out, bias, t, k, n, status, stream, ksplit, b_early);
+  // enough 256 x 256 tiles to keep the CTA pairs busy, and a row count that the 256-row tiles do not pad by much:
+  // the CTA-pair kernel (each CTA stages half of B, a third less shared-memory traffic per MMA)
+  {
+    const int64_t tiles_pair = ((t + 2 * kBM - 1) / (2 * kBM)) * ((n + 255) / 256);
+    const int64_t rows256 = ((t + 255) / 256) * 256, rows128 = ((t + 127) / 128) * 128;
+    if (current_kernel_policy() != 3 && n >= 256 && tiles_pair >= 48 && rows256 * 8 <= rows128 * 9) {
+      const int rc = launch_gemm_sm100_pair(a8, b8, sa, sb, out, std::is_same<OutT, __half>::value ? QO_F16 : QO_BF16, t, k, n,
+                                            acc_out, bias, status, stream);
+      if (rc != QO_ERR_UNSUPPORTED) return rc;
+    }
+  }
   // enough 256 x 256 tiles for every SM: two accumulators per CTA share each B slice
   // (with few tiles and a short K the unshared tile does better: its epilogue overlaps the next main loop and its
   // smaller tiles fill the last wave more evenly)
@@ -833,9 +845,19 @@ int launch_gemm_sm100(const int32_t* a, int64_t lda, const int32_t* b, int64_t b
                       const void* bias, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
   if (workspace_bytes < gemm_sm100_workspace_bytes(t, k, n) || reinterpret_cast<uintptr_t>(workspace) % 256)
     return fail(QO_ERR_WORKSPACE, "int4_matmul: workspace missing, too small or not 256-byte aligned");
+  int rc;
+  // prefill-sized products with K-contiguous operands: the kernel that unpacks the nibbles itself (no widening pass,
+  // the workspace stays untouched)
+  if (gemm_unpack_supported(t, k, n, a, lda, b, bsk, bsn) && gemm_unpack_preferred(t, k, n)) {
+    int dev = 0;
+    QO_CUDA_TRY(cudaGetDevice(&dev));
+    uint32_t* status = device_status_word(dev);
+    if (!status) return fail(QO_ERR_CUDA, "int4_matmul: could not allocate the device status word");
+    rc = launch_gemm_unpack(a, lda, b, bsn, sa, sb, out, out_dtype, t, k, n, acc_out, bias, status, stream);
+    if (rc != QO_ERR_UNSUPPORTED) return rc;
+  }
   int8_t* a8 = reinterpret_cast<int8_t*>(workspace);
   int8_t* b8 = a8 + align256((size_t)t * k);
-  int rc;
   if (bsk == 1 && (k % 32) == 0 && (lda % 4) == 0 && (bsn % 4) == 0 && reinterpret_cast<uintptr_t>(a) % 16 == 0 &&
       reinterpret_cast<uintptr_t>(b) % 16 == 0) {
     // both operands have K contiguous and 16-byte aligned rows: one launch widens both

@@ -175,6 +175,21 @@ int launch_gemm_sm100(const int32_t* a, int64_t lda, const int32_t* b, int64_t b
                       int64_t n, int32_t* acc_out, const void* bias, void* workspace, size_t workspace_bytes,
                       cudaStream_t stream);
 
+// kernel selection of the calling thread (qo_set_kernel_policy): 0 automatic, 1 generic SIMT only, 2 tcgen05 only,
+// 3 tcgen05 only and without the CTA-pair kernel
+int current_kernel_policy();
+// int8 GEMM on CTA pairs (int4_gemm_sm100_pair.cu); QO_ERR_UNSUPPORTED without a message when it does not apply
+int launch_gemm_sm100_pair(const int8_t* a8, const int8_t* b8, const float* sa, const float* sb, void* out, int out_dtype,
+                           int64_t t, int64_t k, int64_t n, int32_t* acc_out, const void* bias, uint32_t* status,
+                           cudaStream_t stream);
+
+// packed-int4 GEMM that unpacks inside the kernel (int4_gemm_sm100_unpack.cu): b is [n, k/8] with row stride ldb words
+bool gemm_unpack_supported(int64_t t, int64_t k, int64_t n, const void* a, int64_t lda, const void* b, int64_t bsk, int64_t bsn);
+bool gemm_unpack_preferred(int64_t t, int64_t k, int64_t n);
+int launch_gemm_unpack(const int32_t* a, int64_t lda, const int32_t* b, int64_t ldb, const float* sa, const float* sb, void* out,
+                       int out_dtype, int64_t t, int64_t k, int64_t n, int32_t* acc_out, const void* bias, uint32_t* status,
+                       cudaStream_t stream);
+
 // pieces of the tcgen05 GEMM, used separately by the fused layer
 int launch_widen_rows(const int32_t* in, int64_t ld_words, int8_t* out, int64_t rows, int64_t k, cudaStream_t stream, bool blocked,
                       bool beside_previous = false);  // beside_previous: may run beside the kernel before it (see int4_gemm_sm100.cu)

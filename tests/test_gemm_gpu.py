@@ -32,6 +32,9 @@ def both_policies(fn):
         return
     assert lib.qo_device_status(stream_ptr()) == N.QO_OK, lib.qo_last_error()
     yield "tcgen05", res
+    res = fn(3)  # the same without the CTA-pair kernels: the single-CTA tcgen05 kernels keep their coverage
+    assert lib.qo_device_status(stream_ptr()) == N.QO_OK, lib.qo_last_error()
+    yield "tcgen05, single CTA", res
 
 
 @pytest.mark.parametrize("name", ["gemm_64x512x96", "gemm_33x256x40"])
@@ -51,7 +54,10 @@ SHAPES = [(1, 64, 8), (1, 4096, 4096), (16, 14336, 512), (128, 256, 256), (129, 
           # 512 tiles of 128 x 256 on 148 SMs, exact and with a ragged last column tile
           (4096, 256, 4096), (4096, 256, 3848),
           # K split over several CTAs per tile: 8 slices of 3 tiles, 2 slices of 8 ragged tiles
-          (64, 8192, 768), (200, 2048, 1000), (100, 4096, 1000)]
+          (64, 8192, 768), (200, 2048, 1000), (100, 4096, 1000),
+          # CTA-pair kernel that unpacks in the kernel: short K with many tiles per pair (the epilogue is the slower side),
+          # a K that is no multiple of 128 (falls back to the widening path), ragged rows and columns
+          (4096, 1024, 9472), (4096, 384, 9472), (3900, 4096, 4104), (4096, 1000 * 8, 4096)]
 
 
 @pytest.mark.parametrize("t,k,n", SHAPES)
