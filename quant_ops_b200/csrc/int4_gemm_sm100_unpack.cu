@@ -16,7 +16,9 @@
 //     needs its own: a stage therefore carries 256 values of K (eight MMAs per pair of commits).
 //   * A barrier probe answers after about 200 cycles even when the phase is long complete: the issuing thread probes
 //     the NEXT stage's barrier before it issues the MMAs of this one and looks at the answer afterwards.
-//   * Tensor memory (512 columns) holds ONE 256-column accumulator and four A stages of 64 columns; the epilogue (8
+//   * A TMA load of a 32 KB stage takes about 1400 cycles from request to arrival (operands in L2), longer than a
+//     stage's MMAs (about 1100): the packed ring is three stages deep, as is the operand ring behind it.
+//   * Tensor memory (512 columns) holds ONE 256-column accumulator and three A stages of 64 columns; the epilogue (8
 //     warps) therefore does not overlap the next tile's main loop, but frees the accumulator as soon as its last
 //     values are in registers.
 //
@@ -26,17 +28,21 @@
 // of K, a dot product does not care, and every product carries the factor 256, which an arithmetic shift removes
 // exactly in the epilogue (|256 * acc| < 2^31 for K <= 131072).  Four integer instructions per eight values.
 //
-// Roles (22 warps per CTA; both CTAs of a pair run the same code, only the leader issues MMAs):
-//   warp 0       TMA producer: packed A block + packed B half into a ring of 2 stages (local barriers)
+// Roles (28 warps per CTA; both CTAs of a pair run the same code, only the leader issues MMAs):
+//   warp 0       TMA producer: packed A block + packed B half into a ring of 3 stages (local barriers)
 //   warp 1       leader: tcgen05.mma.cta_group::2, M = 256, N = 256, eight K = 32 slices per stage; commits release the
 //                operand stage in BOTH CTAs (one commit per CTA, the peer's barrier addressed through mapa)
 //   warps 2-9    epilogue of the CTA's own 128 accumulator rows (two warps per lane quadrant, 128 columns each)
-//   warps 10-17  A converters: two sets of four warps that alternate stages; thread = row, lane quadrant = warp % 4
-//   warps 18-21  B converters: two sets of two warps that alternate stages
+//   warps 10-21  A converters: three sets of four warps, set g takes the stages g, g + 3, ...; thread = row, lane
+//                quadrant = warp % 4
+//   warps 22-27  B converters: three sets of two warps, same rotation
 //   Converters of both CTAs report to the leader's "operands ready" barrier (remote arrivals from the peer).
 //   A converter's work per stage is a chain of fixed latencies (barrier poll, shared-memory loads, the tensor-memory
-//   or shared-memory stores, a proxy fence, the arrival); two sets in rotation keep one chain per set off the
-//   critical path.  Rings of 2 and 4 stages and sets that alternate: a set sees every phase of the barriers it waits on.
+//   or shared-memory stores, a proxy fence, the arrival); sets in rotation keep one chain per set off the critical
+//   path.  There are as many sets as ring slots, so a set always works on the same slot and sees EVERY phase of the
+//   barriers it waits on.  That is required, not a nicety: a parity wait cannot tell use u of a slot from use u - 2, and
+//   TMA loads complete out of order (a box that lies outside the tensor is filled at once), so a set that visited a
+//   slot on every second use only was measured to pass a wait one use early and to release the slot under its readers.
 //
 // Every mbarrier wait is bounded; a wait that runs out records a code in the device status word and its role leaves.
 // The cluster barriers at set-up and tear-down are hardware barriers that every thread of both CTAs reaches.
@@ -54,19 +60,20 @@ constexpr int kBM = 128;        // rows per CTA
 constexpr int kBN = 256;        // columns of the pair's tile
 constexpr int kBNh = kBN / 2;   // B rows staged per CTA
 constexpr int kKStage = 256;    // int4 values per stage = 128 packed bytes = 256 int8 bytes per row
-constexpr int kThreads = 22 * 32;
-constexpr int kPStages = 2;     // packed ring
-constexpr int kOStages = 4;     // operand ring (int8 B in shared memory, A in tensor memory)
+constexpr int kSets = 3;        // converter sets in rotation = ring depth: set g always works on slot g of both rings
+constexpr int kThreads = 28 * 32;
+constexpr int kPStages = kSets;     // packed ring
+constexpr int kOStages = kSets;     // operand ring (int8 B in shared memory, A in tensor memory)
 constexpr int kPABytes = kBM * 128, kPBBytes = kBNh * 128, kPStageBytes = kPABytes + kPBBytes;  // 16 KB + 16 KB
 constexpr int kOAtomBytes = kBNh * 128;                 // one 128-byte K atom of the int8 B half: 16 KB
 constexpr int kOBBytes = 2 * kOAtomBytes;               // 32 KB per operand stage
 constexpr int kOffP = 0;
-constexpr int kOffO = kOffP + kPStages * kPStageBytes;  // 64 KB
-constexpr int kOffSb = kOffO + kOStages * kOBBytes;     // +128 KB; 8 epilogue warps x 128 floats
+constexpr int kOffO = kOffP + kPStages * kPStageBytes;  // 96 KB
+constexpr int kOffSb = kOffO + kOStages * kOBBytes;     // +96 KB; 8 epilogue warps x 128 floats
 constexpr int kOffBar = kOffSb + 8 * 128 * 4;
 constexpr int kSmemBytes = kOffBar + 512 + 1024;
 constexpr int kColA = kBN;      // first tensor-memory column of the A operand stages (64 columns each)
-constexpr int kEpiWarp0 = 2, kAWarp0 = 10, kBWarp0 = 18;
+constexpr int kEpiWarp0 = 2, kAWarp0 = 10, kBWarp0 = 22;
 
 struct Bars {
   uint64_t p_full[kPStages], p_empty[kPStages];
@@ -238,13 +245,16 @@ gemm_s4_unpack_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_co
   } else if (warp < kAWarp0) {
     // ---- epilogue: the CTA's own 128 rows of the tile; warp (q, half) takes columns 128 half .. of lanes 32 q .. ------
     const int q = warp & 3, half = (warp - kEpiWarp0) >> 2;
+    const bool wide_stores = (n % 16) == 0 && (reinterpret_cast<uintptr_t>(out) % 32) == 0;  // rows start on 32-byte boundaries
     float* sb_s = reinterpret_cast<float*>(smem + kOffSb) + (warp - kEpiWarp0) * 128;
     int tile = pair;
     for (int lt = 0; lt < mine; ++lt, tile += npairs) {
       const int mb = tile / tiles_n, nb = tile - mb * tiles_n;
       const int row = mb * 2 * kBM + (int)rank * kBM + q * 32 + lane;
       const bool row_ok = row < t;
-      const float s_row = row_ok ? sa[row] : 0.f;
+      // Both operands carried the factor 16.  float(256 * acc) is exact (|acc| < 2^23) and scaling by a power of two
+      // commutes with rounding, so the factor is taken out of the row scale instead of out of every accumulator.
+      const float s_row = row_ok ? sa[row] * 0.00390625f : 0.f;
       const int colw = nb * kBN + half * 128;  // first column of this warp
       __syncwarp();
       for (int i = lane; i < 128; i += 32) sb_s[i] = (colw + i < n) ? sb[colw + i] : 0.f;
@@ -267,14 +277,12 @@ gemm_s4_unpack_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_co
         }
         const int col0 = colw + cc;
         if (row_ok && col0 < n) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = (uint32_t)((int)v[j] >> 8);  // both operands carried the factor 16
           uint32_t w[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float f0 = ((float)(int)v[2 * j] * s_row) * sb_s[cc + 2 * j];
-            const float f1 = ((float)(int)v[2 * j + 1] * s_row) * sb_s[cc + 2 * j + 1];
-            w[j] = pack_out2<OutT>(f0, f1);
+          for (int j = 0; j < 8; ++j) {
+            const float4 sc = *reinterpret_cast<const float4*>(sb_s + cc + 4 * j);
+            w[2 * j] = pack_out2<OutT>(((float)(int)v[4 * j] * s_row) * sc.x, ((float)(int)v[4 * j + 1] * s_row) * sc.y);
+            w[2 * j + 1] = pack_out2<OutT>(((float)(int)v[4 * j + 2] * s_row) * sc.z, ((float)(int)v[4 * j + 3] * s_row) * sc.w);
           }
           OutT* orow = out + (int64_t)row * n + col0;
           if (bias != nullptr) {
@@ -287,24 +295,36 @@ gemm_s4_unpack_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_co
               }
             }
           }
+          // A lane owns a row, so a warp's store instruction touches 32 different lines; the exposed part of the
+          // epilogue is bound by those line accesses.  32-byte stores (whole sectors) halve their number.
+          if (wide_stores) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            if (col0 + 8 * j < n) reinterpret_cast<uint4*>(orow)[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+            for (int j = 0; j < 2; ++j)
+              if (col0 + 16 * j < n)
+                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(orow + 16 * j), "r"(w[8 * j]), "r"(w[8 * j + 1]),
+                             "r"(w[8 * j + 2]), "r"(w[8 * j + 3]), "r"(w[8 * j + 4]), "r"(w[8 * j + 5]), "r"(w[8 * j + 6]), "r"(w[8 * j + 7]) : "memory");
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (col0 + 8 * j < n) reinterpret_cast<uint4*>(orow)[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+          }
           if (acc_out != nullptr) {
             int32_t* arow = acc_out + (int64_t)row * n + col0;
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-              if (col0 + 4 * j < n) reinterpret_cast<uint4*>(arow)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              if (col0 + 4 * j < n)
+                reinterpret_cast<uint4*>(arow)[j] = make_uint4((uint32_t)((int)v[4 * j] >> 8), (uint32_t)((int)v[4 * j + 1] >> 8),
+                                                               (uint32_t)((int)v[4 * j + 2] >> 8), (uint32_t)((int)v[4 * j + 3] >> 8));
           }
         }
         __syncwarp();
       }
     }
   } else if (warp < kBWarp0) {
-    // ---- A converters: set e takes the stages with (step & 1) == e; thread = one row of the CTA's A block -----------
-    const int e = (warp - kAWarp0) >> 2, q = warp & 3, r = q * 32 + lane;
+    // ---- A converters: set e takes the stages e, e + 3, ...; thread = one row of the CTA's A block ---------------------
+    const int e = (warp - kAWarp0) >> 2, q = warp & 3, r = q * 32 + lane;  // set 0 .. 2
     const uint32_t row_off = (uint32_t)(r * 128), sw = (uint32_t)(r & 7);
-    for (int step = e; step < total_steps; step += 2) {
+    for (int step = e; step < total_steps; step += kSets) {
       const int ps = step % kPStages, pph = (step / kPStages) & 1;
       const int s = step % kOStages, ph = (step / kOStages) & 1;
       if (__any_sync(0xffffffffu, mbar_wait2(smem_u32(&bars->p_full[ps]), pph, smem_u32(&bars->op_empty[s]), ph ^ 1) != 0)) {
@@ -344,8 +364,8 @@ gemm_s4_unpack_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_co
     // ---- B converters: 128 rows x 8 packed 16-byte pieces per stage, sixteen per thread of the set on duty; eight
     // consecutive lanes take eight consecutive rows of one piece, which is conflict-free for the 128-byte-swizzled
     // reads and writes ---------------------------------------------------------------------------------------------
-    const int f = (warp - kBWarp0) >> 1, bt = ((warp - kBWarp0) & 1) * 32 + lane;  // set, thread within the set (0 .. 63)
-    for (int step = f; step < total_steps; step += 2) {
+    const int f = (warp - kBWarp0) >> 1, bt = ((warp - kBWarp0) & 1) * 32 + lane;  // set 0 .. 2, thread within the set (0 .. 63)
+    for (int step = f; step < total_steps; step += kSets) {
       const int ps = step % kPStages, pph = (step / kPStages) & 1;
       const int s = step % kOStages, ph = (step / kOStages) & 1;
       if (__any_sync(0xffffffffu, mbar_wait2(smem_u32(&bars->p_full[ps]), pph, smem_u32(&bars->op_empty[s]), ph ^ 1) != 0)) {
