@@ -377,8 +377,11 @@ int qo_w4a4_linear_prepared(const void* x, int64_t ldx, const void* left, const 
     workspace_bytes = need;
   }
   if (workspace_bytes < need) return fail(QO_ERR_WORKSPACE, "w4a4_linear: workspace of %zu bytes, need %zu", workspace_bytes, need);
-  // few tokens (weight-streaming kernel), or a shape / policy the int8 tensor-core kernel does not take: packed route
-  const bool direct = t_policy != 1 && tokens > 32 && gemm_sm100_supported(tokens, k, n_out, k / 8, 1, k / 8) &&
+  // few tokens (weight-streaming kernel), prefill sizes (the GEMM that unpacks in the kernel is the faster one there and
+  // needs no int8 copy), or a shape / policy the int8 tensor-core kernel does not take: packed route
+  const bool unpack_route = t_policy != 1 && gemm_unpack_preferred(tokens, k, n_out) &&
+                            gemm_unpack_supported(tokens, k, n_out, workspace, k / 8, w_packed, 1, k / 8);
+  const bool direct = !unpack_route && t_policy != 1 && tokens > 32 && gemm_sm100_supported(tokens, k, n_out, k / 8, 1, k / 8) &&
                       reinterpret_cast<uintptr_t>(prepared) % 256 == 0;
   if (!direct)
     return qo_w4a4_linear(x, ldx, left, right, w_packed, w_scale, bias, out, tokens, m, n, n_out, clip_ratio, in_dtype, out_dtype,

@@ -11,8 +11,11 @@
 //   warp 2       issues Z = LL . Y2      A = LL = 2 copies of L^T, each starting on a 32-row boundary; staged as the
 //                                        rows of L laid along M (M-major), so neither transform is transposed;
 //                                        B = the 2 tokens' Y side by side along N (N-major, N = 128), K = M
-//   warps 3-10   Y pass: tensor memory -> round to the activation dtype -> shared memory in the B layout;
-//                warp (q, h) handles columns 32h..32h+31 of tensor-memory lanes 32q..32q+31
+//   warps 3-10   Y pass: tensor memory -> round to the activation dtype -> shared memory in the B layout; two sets of
+//                four warps that alternate between groups (a group's trip through this pass is a chain of fixed
+//                latencies -- barrier poll, tensor-memory load, proxy fence, arrival -- of about the time the rest of
+//                the pipeline needs per group; one set working on every group was the kernel's serial bottleneck);
+//                warp q of a set handles all 64 columns of tensor-memory lanes 32q..32q+31, 32 at a time
 //   warps 11-26  quantize pass, two sets of 8 warps that alternate between groups; lane block c of a set holds a copy
 //                of the Z rows and serves token c; a thread rounds its 32 values once (packed pairs), the token's
 //                absmax is combined through shared memory, then scale, int4 codes and one 16-byte store
@@ -39,7 +42,7 @@ constexpr int kThreads = 864;                  // 27 warps: TMA, two MMA issuers
 constexpr int kEpi1Warp0 = 3, kEpi2Warp0 = 11; // first warp of the Y pass / of the two quantize sets
 constexpr int kGroup = 2;                      // tokens per group
 constexpr int kXStages = 6;
-constexpr int kYStages = 3;                    // also the number of Y accumulator stages
+constexpr int kYStages = 4;                    // also the number of Y accumulator stages; even: each Y-pass set owns two
 constexpr int kStageBytes = 128 * 128;         // up to 2 x 64 rows of 128 bytes
 constexpr int kOffX = 0;
 constexpr int kOffY = kOffX + kXStages * kStageBytes;
@@ -47,7 +50,7 @@ constexpr int kOffR = kOffY + kYStages * kStageBytes;
 constexpr int kOffLL = kOffR + 64 * 128;
 constexpr int kOffMisc = kOffLL + kAtomBytes;
 constexpr int kSmemBytes = kOffMisc + 1024 + 1024;
-constexpr int kTmemCols = 512;                 // Y accumulators: 3 stages x 64 columns; Z accumulators: 2 stages x 128
+constexpr int kTmemCols = 512;                 // Y accumulators: 4 stages x 64 columns; Z accumulators: 2 stages x 128
 constexpr int kColZ = 256;
 
 struct Misc {
@@ -90,8 +93,8 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
     for (int i = 0; i < kXStages; ++i) { mbar_init(smem_u32(&misc->full_x[i]), 1); mbar_init(smem_u32(&misc->empty_x[i]), 1); }
     for (int i = 0; i < kYStages; ++i) {
       mbar_init(smem_u32(&misc->d1_full[i]), 1);
-      mbar_init(smem_u32(&misc->d1_empty[i]), 2 * nq1);  // one arrival per working warp of the Y pass
-      mbar_init(smem_u32(&misc->y_full[i]), 2 * nq1);
+      mbar_init(smem_u32(&misc->d1_empty[i]), nq1);  // one arrival per working warp of the Y-pass set on duty
+      mbar_init(smem_u32(&misc->y_full[i]), nq1);
       mbar_init(smem_u32(&misc->y_empty[i]), 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -219,36 +222,40 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       }
     }
   } else if (warp < kEpi2Warp0) {
-    // ---- Y pass: 8 warps; warp (q, h) converts columns 32h .. 32h+31 of tensor-memory lanes 32q .. 32q+31 ------
-    const int q = warp & 3, h = (warp - kEpi1Warp0) >> 2, r = q * 32 + lane;
-    int s = 0, ph = 0;
-    for (int it = 0; it < (q < nq1 ? mine : 0); ++it) {
+    // ---- Y pass: set e (4 warps) takes the groups with (it & 1) == e; warp q converts lanes 32q .. 32q+31 ------------
+    const int q = warp & 3, e = (warp - kEpi1Warp0) >> 2, r = q * 32 + lane;
+    for (int it = e; it < (q < nq1 ? mine : 0); it += 2) {
+      const int s = it % kYStages, ph = (it / kYStages) & 1;  // kYStages is even: a set sees every phase of its stages
       if (__any_sync(0xffffffffu, mbar_wait2(smem_u32(&misc->d1_full[s]), ph, smem_u32(&misc->y_empty[s]), ph ^ 1) != 0)) {
         atomicCAS(status, 0u, 0x700u + s);
         break;
       }
       tc_fence_after();
-      uint32_t v[32];
-      tmem_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + s * 64 + h * 32, v);
-      tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive_warp(smem_u32(&misc->d1_empty[s]));  // accumulators are in registers: the stage can be overwritten
-      if (r < rows_group) {
-        const int yr = r < m ? r : r - m + k2;  // row of the Y stage: token c's rows start at c * k2
-        uint8_t* yrow = smem + kOffY + s * kStageBytes + yr * 128;
+      const int yr = r < m ? r : r - m + k2;  // row of the Y stage: token c's rows start at c * k2
+      uint8_t* yrow = smem + kOffY + s * kStageBytes + yr * 128;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4 w;
-          w.x = pack2<T>(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
-          w.y = pack2<T>(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
-          w.z = pack2<T>(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
-          w.w = pack2<T>(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
-          *reinterpret_cast<uint4*>(yrow + (((h * 4 + j) ^ (yr & 7)) << 4)) = w;
+      for (int h = 0; h < 2; ++h) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + s * 64 + h * 32, v);
+        tmem_ld_wait();
+        if (h == 1) {
+          tc_fence_before();
+          mbar_arrive_warp(smem_u32(&misc->d1_empty[s]));  // accumulators are in registers: the stage can be overwritten
+        }
+        if (r < rows_group) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 w;
+            w.x = pack2<T>(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+            w.y = pack2<T>(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+            w.z = pack2<T>(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+            w.w = pack2<T>(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+            *reinterpret_cast<uint4*>(yrow + (((h * 4 + j) ^ (yr & 7)) << 4)) = w;
+          }
         }
       }
       fence_proxy_async_smem();
       mbar_arrive_warp(smem_u32(&misc->y_full[s]));
-      if (++s == kYStages) { s = 0; ph ^= 1; }
     }
   } else {
     // ---- quantize pass ---------------------------------------------------------------------------------------
