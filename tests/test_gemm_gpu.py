@@ -346,3 +346,23 @@ def test_projection_stack_slice_against_the_oracle(name, k, n_out):
     aq, sa = abi_quantize(xd, ld, rd, 0.9, True, "bf16")
     assert_layer_close(t2f(kept)[rows], ref, O.unpack_int32_to_int4(aq.cpu().numpy()[rows]), O.unpack_int32_to_int4(rc),
                        t2f(sa)[rows], rs)
+
+
+@pytest.mark.parametrize("tokens,k,n_out", [(1, 4096, 4096), (7, 4096, 14336), (16, 4096, 1024), (20, 14336, 4096), (32, 4096, 11008), (3, 4096, 200)])
+def test_fused_layer_decode_shapes(tokens, k, n_out):
+    """Decode-sized fused layer over the projection shapes: inside the layer the GEMM keeps its weight rows resident in
+    shared memory (fetched beside the quantizer); bit-equal to quantize -> GEMM through the two separate entry points,
+    whose GEMM is the weight-streaming kernel."""
+    x, left, right = make_inputs(tokens, k, "bf16", 777 + tokens + n_out, True)
+    g = torch.Generator().manual_seed(n_out)
+    wq = torch.randint(-8, 8, (n_out, k), generator=g, dtype=torch.int8)
+    wpd = torch.from_numpy(O.pack_int4_to_int32(wq.numpy())).to(DEV)
+    swd = (torch.rand(n_out, generator=g) * 0.01 + 0.001).to(DEV)
+    bias = (torch.randn(n_out, generator=g) * 0.1).bfloat16().to(DEV)
+    xd, ld, rd = x.to(DEV), left.to(DEV), right.to(DEV)
+    out = abi_linear(xd, ld, rd, wpd, swd, bias, 0.9, "bf16", "bf16")
+    assert lib.qo_device_status(stream_ptr()) == N.QO_OK, lib.qo_last_error()
+    aq, sa = abi_quantize(xd, ld, rd, 0.9, True, "bf16")
+    two_call, acc = abi_int4_matmul(aq, wpd.t(), sa, swd, "bf16", True)
+    np.testing.assert_array_equal(acc.cpu().numpy(), O.int4_accumulators(aq.cpu().numpy(), wpd.cpu().numpy().T))
+    assert torch.equal(out, (two_call.float() + bias.float()).bfloat16())
