@@ -757,6 +757,8 @@ def top_level(rec, env_world, args, metric, dtype, scaling, extra_config=None):
             cfg[key] = rec.pop(key)
     if extra_config:
         cfg.update(extra_config)
+    if getattr(args, "policy", 0):
+        cfg["kernel_policy"] = args.policy
     out = {"metric": metric, "value": rec.pop("value"), "unit": rec.pop("unit"), "n_gpus": env_world, "steps": args.steps,
            "warmup": max(3, args.warmup), "ms_per_step": rec.pop("ms_per_step"), "higher_is_better": True, "scaling": scaling,
            "vs_baseline": None, "dtype": dtype, "data": "synthetic", "config": cfg}
@@ -766,6 +768,8 @@ def top_level(rec, env_world, args, metric, dtype, scaling, extra_config=None):
 
 def run_ours(args):
     env = Env()
+    if args.policy:
+        env.nat.check(env.lib.qo_set_kernel_policy(args.policy))
     wl = args.workload
     line = None
     if wl in ("all", "quantize"):
@@ -913,6 +917,9 @@ def main():
     ap.add_argument("--tokens", type=int, default=None, help="rows of the `linear` (default 16) and `quantize_tokens` (default 65536) workloads")
     ap.add_argument("--n-out", type=int, default=None, help="output channels of the `gemm` workload (default 4096)")
     ap.add_argument("--prepared", action="store_true", help="`linear`: weights also kept widened to int8 (qo_prepare_weights)")
+    ap.add_argument("--policy", type=int, default=0, choices=[0, 2, 3],
+                    help="kernel selection (qo_set_kernel_policy): 0 automatic, 2 tcgen05 kernels only, 3 tcgen05 kernels "
+                         "without the CTA-pair GEMMs (the single-CTA kernels the pair kernels replaced)")
     args = ap.parse_args()
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
         # started by hand rather than by torchrun: start one rank per GPU ourselves
