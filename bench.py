@@ -457,7 +457,9 @@ def gemm_records(env: Env, args, n_outs):
                     "value": tops, "unit": "TOP/s", "graph_ms_per_step": None if graph_ms is None else graph_ms / args.sub_steps,
                     "kernel": {1: "generic SIMT", 2: "tcgen05", 3: "weight-streaming"}.get(lib.qo_last_gemm_path(), "?"),
                     "parity_vs_oracle_sample": parity_ok, "l2": f"weights rotate over {nw} buffers",
-                    "path": "packed operands by TMA, nibbles unpacked in the kernel (A through tensor memory, B in shared memory), no workspace use",
+                    "path": ("packed operands by TMA, nibbles unpacked in the kernel (A through tensor memory, B in shared memory), no workspace use"
+                             if launches == args.sub_steps else
+                             "widening pass (nibbles -> int8 in the workspace) + int8 tensor-core kernel on single CTAs"),
                     "roofline": tensor_roofline(env, tops, ops), "gpu_launches": launches, "clocks": clocks})
         # the library GEMM on already widened int8 operands, for comparison in the same run (not part of the product path)
         try:
