@@ -122,33 +122,43 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
     // M-major A operand (row k of L laid along M, once per token copy), so nothing is transposed here.
     constexpr int kStagers = kThreads - 32;
     const int t13 = tid - 32;
+    // Every thread first requests all its pieces of both transforms (at most three each) and only then stores them: the
+    // loads come from L2 with several hundred cycles of latency each, and this staging is on the path of the first tile.
     // R: rows k < nc, 16 pieces per row; columns past nc are zero (the first product always has N = 128)
-    for (int idx = t13; idx < nc * 16; idx += kStagers) {
-      const int k = idx >> 4, c = idx & 15;
-      uint4 w = make_uint4(0, 0, 0, 0);
-      if (8 * c < nc) w = *reinterpret_cast<const uint4*>(right + k * nc + 8 * c);
-      *reinterpret_cast<uint4*>(smem + kOffR + (c >> 3) * kAtomBytes + k * 128 + (((c & 7) ^ (k & 7)) << 4)) = w;
-    }
     // LL: rows k < k2 (rows m .. k2-1 pad the reduction length and must be zero), M position copy * mpad + i holds
     // L[k][i]; every other M position of these rows is zero
+    static_assert(3 * kStagers >= 128 * 16, "three pieces per thread cover a transform");
     const int mpad = (m + 31) & ~31;  // the second copy starts on a 32-row boundary: a warp reads one token's columns
     const bool l_vec = (m & 7) == 0;  // rows of L start on 16-byte boundaries
-    for (int idx = t13; idx < k2 * 16; idx += kStagers) {
-      const int k = idx >> 4, c = idx & 15;
+    uint4 wr[3], wl[3];
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+      const int idx = t13 + j * kStagers, k = idx >> 4, c = idx & 15;
+      wr[j] = make_uint4(0, 0, 0, 0);
+      if (idx < nc * 16 && 8 * c < nc) wr[j] = *reinterpret_cast<const uint4*>(right + k * nc + 8 * c);
+    }
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+      const int idx = t13 + j * kStagers, k = idx >> 4, c = idx & 15;
       const int cpy = (8 * c) / mpad, i0 = 8 * c - cpy * mpad;
-      uint4 w = make_uint4(0, 0, 0, 0);
-      if (k < m && cpy < group && i0 < m) {
+      wl[j] = make_uint4(0, 0, 0, 0);
+      if (idx < k2 * 16 && k < m && cpy < group && i0 < m) {
         const T* src = left + k * m + i0;
         if (l_vec) {
-          w = *reinterpret_cast<const uint4*>(src);
+          wl[j] = *reinterpret_cast<const uint4*>(src);
         } else {
           uint32_t e[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) e[j] = i0 + j < m ? (uint32_t)reinterpret_cast<const uint16_t*>(src)[j] : 0u;
-          w = make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
+          for (int i = 0; i < 8; ++i) e[i] = i0 + i < m ? (uint32_t)reinterpret_cast<const uint16_t*>(src)[i] : 0u;
+          wl[j] = make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
         }
       }
-      *reinterpret_cast<uint4*>(smem + kOffLL + (c >> 3) * kAtomBytes + k * 128 + (((c & 7) ^ (k & 7)) << 4)) = w;
+    }
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+      const int idx = t13 + j * kStagers, k = idx >> 4, c = idx & 15;
+      if (idx < nc * 16) *reinterpret_cast<uint4*>(smem + kOffR + (c >> 3) * kAtomBytes + k * 128 + (((c & 7) ^ (k & 7)) << 4)) = wr[j];
+      if (idx < k2 * 16) *reinterpret_cast<uint4*>(smem + kOffLL + (c >> 3) * kAtomBytes + k * 128 + (((c & 7) ^ (k & 7)) << 4)) = wl[j];
     }
     fence_proxy_async_smem();
     asm volatile("bar.sync 1, %0;" ::"n"(kStagers) : "memory");

@@ -127,21 +127,33 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
     // laid along M, once per token copy), so nothing is transposed here.
     constexpr int kStagers = kThreads - 32;
     const int t13 = tid - 32;
+    // Every thread first requests all its pieces of both transforms (one of R, at most two of LL) and only then stores
+    // them: the loads come from L2 with several hundred cycles of latency each, and this staging is on the path of the
+    // first group.
     // R: rows k < nc, 8 pieces per row; columns past nc are zero (the first product always has N = 64)
-    for (int idx = t13; idx < nc * 8; idx += kStagers) {
-      const int k = idx >> 3, c = idx & 7;
-      uint4 w = make_uint4(0, 0, 0, 0);
-      if (8 * c < nc) w = *reinterpret_cast<const uint4*>(right + k * nc + 8 * c);
-      *reinterpret_cast<uint4*>(smem + kOffR + k * 128 + ((c ^ (k & 7)) << 4)) = w;
-    }
     // LL: rows k < k2 (rows m .. k2-1 pad the reduction length and must be zero), M position copy * mpad + i holds
     // L[k][i]; every other M position of these rows is zero.  M is a multiple of 8: pieces are whole or empty.
-    for (int idx = t13; idx < k2 * 16; idx += kStagers) {
-      const int k = idx >> 4, c = idx & 15;
+    static_assert(kStagers >= 64 * 8 && 2 * kStagers >= 64 * 16, "one piece of R and two of LL per thread cover the transforms");
+    uint4 wr = make_uint4(0, 0, 0, 0), wl[2];
+    {
+      const int k = t13 >> 3, c = t13 & 7;
+      if (t13 < nc * 8 && 8 * c < nc) wr = *reinterpret_cast<const uint4*>(right + k * nc + 8 * c);
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int idx = t13 + j * kStagers, k = idx >> 4, c = idx & 15;
       const int cpy = (8 * c) / mpad, i0 = 8 * c - cpy * mpad;
-      uint4 w = make_uint4(0, 0, 0, 0);
-      if (k < m && cpy < kGroup && i0 < m) w = *reinterpret_cast<const uint4*>(left + k * m + i0);
-      *reinterpret_cast<uint4*>(smem + kOffLL + (c >> 3) * (kAtomBytes / 2) + k * 128 + (((c & 7) ^ (k & 7)) << 4)) = w;
+      wl[j] = make_uint4(0, 0, 0, 0);
+      if (idx < k2 * 16 && k < m && cpy < kGroup && i0 < m) wl[j] = *reinterpret_cast<const uint4*>(left + k * m + i0);
+    }
+    if (t13 < nc * 8) {
+      const int k = t13 >> 3, c = t13 & 7;
+      *reinterpret_cast<uint4*>(smem + kOffR + k * 128 + ((c ^ (k & 7)) << 4)) = wr;
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int idx = t13 + j * kStagers, k = idx >> 4, c = idx & 15;
+      if (idx < k2 * 16) *reinterpret_cast<uint4*>(smem + kOffLL + (c >> 3) * (kAtomBytes / 2) + k * 128 + (((c & 7) ^ (k & 7)) << 4)) = wl[j];
     }
     if (k2 != m) {
       // M is not a multiple of 16: rows m .. k2-1 of each token's Y block only pad the reduction; they are zeroed once
