@@ -59,7 +59,11 @@ def test_argument_validation_needs_no_gpu():
     # empty problems succeed without touching a device
     assert lib.qo_flatquant_quantize(None, 16, None, None, None, None, 0, 4, 4, 1.0, N.QO_BF16, 0, N.QO_F32, None) == N.QO_OK
     assert lib.qo_int4_matmul(None, 1, None, 1, 1, None, None, None, N.QO_F16, 0, 8, 4, None, None, 0, None) == N.QO_OK
-    assert lib.qo_set_kernel_policy(3) == N.QO_ERR_INVALID_ARGUMENT
+    # kernel policies 0 .. 3 exist; the setting is per thread and is put back
+    assert lib.qo_set_kernel_policy(4) == N.QO_ERR_INVALID_ARGUMENT
+    assert lib.qo_set_kernel_policy(-1) == N.QO_ERR_INVALID_ARGUMENT
+    assert lib.qo_set_kernel_policy(3) == N.QO_OK
+    assert lib.qo_set_kernel_policy(0) == N.QO_OK
 
 
 def test_compute_without_gpu_fails_loudly():
