@@ -251,12 +251,8 @@ int4_gemm_resident_kernel(const uint32_t* __restrict__ a, int64_t lda, const uin
     for (int nt = 0; nt < NT; ++nt)
       x[nt] = (tok_ok[nt] && c < ce) ? __ldg(reinterpret_cast<const uint4*>(a + (int64_t)(nt * 8 + g) * lda + (int64_t)c * kChunkWords + 4 * t4)) : zero4;
   };
-  // the codes of kDepth chunks are in flight per warp (they come from L2, several hundred cycles away, and a warp has
-  // only about seven chunks): the first ones are requested while the last weight rows may still be arriving
-  constexpr int kDepth = NT <= 2 ? 4 : 2;
-  uint4 xq[kDepth][NT];
-#pragma unroll
-  for (int d = 0; d < kDepth; ++d) load_x(xq[d], cb + d);
+  uint4 xa[NT], xb[NT];
+  load_x(xa, cb);  // the first codes are requested while the last weight rows may still be arriving
 
   const bool landed = ptx::mbar_wait(bar_a, 0);
   if (!__syncthreads_and(landed)) {  // one decision for the whole CTA
@@ -296,12 +292,11 @@ int4_gemm_resident_kernel(const uint32_t* __restrict__ a, int64_t lda, const uin
       }
     }
   };
-  for (int c = cb; c < ce; c += kDepth) {
-#pragma unroll
-    for (int d = 0; d < kDepth; ++d) {
-      compute(xq[d], c + d);
-      load_x(xq[d], c + d + kDepth);
-    }
+  for (int c = cb; c < ce; c += 2) {
+    load_x(xb, c + 1);
+    compute(xa, c);
+    load_x(xa, c + 2);
+    compute(xb, c + 1);
   }
 
   // partial sums of the 16 warps through the shared memory that held the weights
