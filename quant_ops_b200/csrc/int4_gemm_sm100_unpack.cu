@@ -157,7 +157,7 @@ template <typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_s4_unpack_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
                       const float* __restrict__ sa, const float* __restrict__ sb, OutT* __restrict__ out,
-                      int32_t* __restrict__ acc_out, const OutT* __restrict__ bias, int t, int n, int k,
+                      int32_t* __restrict__ acc_out, const OutT* __restrict__ bias, int t, int n, int k, int items, int cut_from,
                       uint32_t* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -166,11 +166,20 @@ gemm_s4_unpack_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_co
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t rank = cluster_cta_rank();  // 0 = leader
   const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
-  const int tiles_n = (n + kBN - 1) / kBN, tiles_m = (t + 2 * kBM - 1) / (2 * kBM);
-  const int ntiles = tiles_m * tiles_n, ksteps = k / kKStage;  // k is a multiple of 256 (checked by the host)
-  int mine = 0;                              // tiles of this pair
-  if (pair < ntiles) mine = (ntiles - pair + npairs - 1) / npairs;
+  const int tiles_n = (n + kBN - 1) / kBN;
+  const int ksteps = k / kKStage;  // k is a multiple of 256 (checked by the host)
+  // Work items: whole tiles, except that the tiles of a last wave which would occupy at most half of the pairs are cut
+  // into two halves of 128 columns (MMAs with N = 128), so that twice as many pairs share that wave: 256 tiles on 74
+  // pairs take the time of 3.7 tiles instead of 4.
+  // (items and cut_from, the first item that is a half, come from the host: kernel parameters cost no registers)
+  int mine = 0;                              // items of this pair
+  if (pair < items) mine = (items - pair + npairs - 1) / npairs;
   const int total_steps = mine * ksteps;
+  // item -> tile index, first column of the item inside the tile (0 or 128), columns of the item (256 or 128)
+  auto item_of = [&](int item, int& tile, int& col_in_tile, int& width) {
+    if (item < cut_from) { tile = item; col_in_tile = 0; width = kBN; }
+    else { tile = cut_from + ((item - cut_from) >> 1); col_in_tile = ((item - cut_from) & 1) * (kBN / 2); width = kBN / 2; }
+  };
 
   if (tid == 0) {
     for (int i = 0; i < kPStages; ++i) { mbar_init(smem_u32(&bars->p_full[i]), 1); mbar_init(smem_u32(&bars->p_empty[i]), 6); }
@@ -198,9 +207,12 @@ gemm_s4_unpack_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_co
     if (lane == 0) {
       int step = 0;
       bool ok = true;
-      for (int tile = pair; ok && tile < ntiles; tile += npairs) {
+      for (int item = pair; ok && item < items; item += npairs) {
+        int tile, col_in_tile, width;
+        item_of(item, tile, col_in_tile, width);
         const int mb = tile / tiles_n, nb = tile - mb * tiles_n;
-        const int row_a = mb * 2 * kBM + (int)rank * kBM, row_b = nb * kBN + (int)rank * kBNh;
+        // a CTA stages its half of the item's B rows; the box always has 128 rows, of which a half item uses the first 64
+        const int row_a = mb * 2 * kBM + (int)rank * kBM, row_b = nb * kBN + col_in_tile + (int)rank * (width >> 1);
         for (int ks = 0; ks < ksteps; ++ks, ++step) {
           const int ps = step % kPStages, pph = (step / kPStages) & 1;
           if (!mbar_wait(smem_u32(&bars->p_empty[ps]), pph ^ 1)) { atomicCAS(status, 0u, 0xA00u + ps); ok = false; break; }
@@ -215,7 +227,8 @@ gemm_s4_unpack_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_co
   } else if (warp == 1) {
     // ---- MMA issuer (leader CTA only) ----------------------------------------------------------------------------
     if (lane == 0 && rank == 0) {
-      const uint32_t idesc = umma_idesc(2, 1, 1, 0, 0, 2 * kBM, kBN);  // s32 accumulators, s8 x s8, K-major, M = 256 over the pair
+      const uint32_t idesc_whole = umma_idesc(2, 1, 1, 0, 0, 2 * kBM, kBN);  // s32 accumulators, s8 x s8, K-major, M = 256 over the pair
+      const uint32_t idesc_half = umma_idesc(2, 1, 1, 0, 0, 2 * kBM, kBN / 2);
       // one thread feeds the tensor cores of both SMs, so its instruction count per MMA matters: the B descriptor is
       // built once and advanced by adding to its address field (units of 16 bytes)
       const uint64_t b_desc0 = umma_smem_desc_sw128(smem_base + kOffO, 16, 1024);
@@ -225,6 +238,7 @@ gemm_s4_unpack_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_co
       bool ok = true, ready = false;  // ready: the operands of `step` were already seen complete by an early probe
       for (int lt = 0; ok && lt < mine; ++lt) {
         if (!mbar_wait(smem_u32(&bars->acc_empty), (lt & 1) ^ 1)) { atomicCAS(status, 0u, 0xA10u); break; }
+        const uint32_t idesc = pair + lt * npairs >= cut_from ? idesc_half : idesc_whole;
         for (int ks = 0; ks < ksteps; ++ks, ++step) {
           const int s = step % kOStages, ph = (step / kOStages) & 1;
           if (!ready && !mbar_wait(smem_u32(&bars->op_ready[s]), ph)) { atomicCAS(status, 0u, 0xA20u + s); ok = false; break; }
@@ -247,26 +261,28 @@ gemm_s4_unpack_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_co
     const int q = warp & 3, half = (warp - kEpiWarp0) >> 2;
     const bool wide_stores = (n % 16) == 0 && (reinterpret_cast<uintptr_t>(out) % 32) == 0;  // rows start on 32-byte boundaries
     float* sb_s = reinterpret_cast<float*>(smem + kOffSb) + (warp - kEpiWarp0) * 128;
-    int tile = pair;
-    for (int lt = 0; lt < mine; ++lt, tile += npairs) {
+    for (int lt = 0; lt < mine; ++lt) {
+      int tile, col_in_tile, width;
+      item_of(pair + lt * npairs, tile, col_in_tile, width);
       const int mb = tile / tiles_n, nb = tile - mb * tiles_n;
+      const int wcols = width >> 1;  // columns of this warp: 128, or 64 of a half item
       const int row = mb * 2 * kBM + (int)rank * kBM + q * 32 + lane;
       const bool row_ok = row < t;
       // Both operands carried the factor 16.  float(256 * acc) is exact (|acc| < 2^23) and scaling by a power of two
       // commutes with rounding, so the factor is taken out of the row scale instead of out of every accumulator.
       const float s_row = row_ok ? sa[row] * 0.00390625f : 0.f;
-      const int colw = nb * kBN + half * 128;  // first column of this warp
+      const int colw = nb * kBN + col_in_tile + half * wcols;  // first column of this warp
       __syncwarp();
-      for (int i = lane; i < 128; i += 32) sb_s[i] = (colw + i < n) ? sb[colw + i] : 0.f;
+      for (int i = lane; i < wcols; i += 32) sb_s[i] = (colw + i < n) ? sb[colw + i] : 0.f;
       __syncwarp();
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->acc_full), lt & 1))) { atomicCAS(status, 0u, 0xA30u); break; }
       tc_fence_after();
 #pragma unroll 1
-      for (int cc = 0; cc < 128; cc += 32) {
+      for (int cc = 0; cc < wcols; cc += 32) {
         uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + half * 128 + cc, v);
+        tmem_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + half * wcols + cc, v);
         tmem_ld_wait();
-        if (cc == 96) {
+        if (cc + 32 == wcols) {
           // the last accumulator values of this warp are in registers: the next tile's MMAs may overwrite them
           tc_fence_before();
           __syncwarp();
@@ -277,36 +293,38 @@ gemm_s4_unpack_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_co
         }
         const int col0 = colw + cc;
         if (row_ok && col0 < n) {
-          uint32_t w[16];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float4 sc = *reinterpret_cast<const float4*>(sb_s + cc + 4 * j);
-            w[2 * j] = pack_out2<OutT>(((float)(int)v[4 * j] * s_row) * sc.x, ((float)(int)v[4 * j + 1] * s_row) * sc.y);
-            w[2 * j + 1] = pack_out2<OutT>(((float)(int)v[4 * j + 2] * s_row) * sc.z, ((float)(int)v[4 * j + 3] * s_row) * sc.w);
-          }
           OutT* orow = out + (int64_t)row * n + col0;
-          if (bias != nullptr) {
+          // 16 columns at a time: eight packed words live beside the 32 accumulators, not sixteen
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              if (col0 + 2 * j < n) {
-                const float2 o = unpack_out2(w[j], OutT());
-                const float2 b = unpack_out2(*reinterpret_cast<const uint32_t*>(bias + col0 + 2 * j), OutT());
-                w[j] = pack_out2<OutT>(o.x + b.x, o.y + b.y);
+          for (int jh = 0; jh < 2; ++jh) {
+            if (col0 + 16 * jh >= n) break;
+            uint32_t w[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float4 sc = *reinterpret_cast<const float4*>(sb_s + cc + 16 * jh + 4 * j);
+              const uint32_t* vv = v + 16 * jh + 4 * j;
+              w[2 * j] = pack_out2<OutT>(((float)(int)vv[0] * s_row) * sc.x, ((float)(int)vv[1] * s_row) * sc.y);
+              w[2 * j + 1] = pack_out2<OutT>(((float)(int)vv[2] * s_row) * sc.z, ((float)(int)vv[3] * s_row) * sc.w);
+            }
+            if (bias != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                if (col0 + 16 * jh + 2 * j < n) {
+                  const float2 o = unpack_out2(w[j], OutT());
+                  const float2 bb = unpack_out2(*reinterpret_cast<const uint32_t*>(bias + col0 + 16 * jh + 2 * j), OutT());
+                  w[j] = pack_out2<OutT>(o.x + bb.x, o.y + bb.y);
+                }
               }
             }
-          }
-          // A lane owns a row, so a warp's store instruction touches 32 different lines; the exposed part of the
-          // epilogue is bound by those line accesses.  32-byte stores (whole sectors) halve their number.
-          if (wide_stores) {
-#pragma unroll
-            for (int j = 0; j < 2; ++j)
-              if (col0 + 16 * j < n)
-                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(orow + 16 * j), "r"(w[8 * j]), "r"(w[8 * j + 1]),
-                             "r"(w[8 * j + 2]), "r"(w[8 * j + 3]), "r"(w[8 * j + 4]), "r"(w[8 * j + 5]), "r"(w[8 * j + 6]), "r"(w[8 * j + 7]) : "memory");
-          } else {
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              if (col0 + 8 * j < n) reinterpret_cast<uint4*>(orow)[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+            // A lane owns a row, so a warp's store instruction touches 32 different lines; the exposed part of the
+            // epilogue is bound by those line accesses.  32-byte stores (whole sectors) halve their number.
+            if (wide_stores) {
+              asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(orow + 16 * jh), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                           "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+            } else {
+              reinterpret_cast<uint4*>(orow + 16 * jh)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+              if (col0 + 16 * jh + 8 < n) reinterpret_cast<uint4*>(orow + 16 * jh)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            }
           }
           if (acc_out != nullptr) {
             int32_t* arow = acc_out + (int64_t)row * n + col0;
@@ -498,6 +516,10 @@ int launch_typed(const int32_t* a, int64_t lda, const int32_t* b, int64_t ldb, c
   if ((rc = make_map_packed(&b_map, b, n, k, ldb, kBNh))) return rc;
   const int64_t ntiles = ((t + 2 * kBM - 1) / (2 * kBM)) * ((n + kBN - 1) / kBN);
   const int pairs = (int)(ntiles < pairs_max ? ntiles : pairs_max);
+  // tiles of a last wave that would occupy at most half of the pairs are cut into halves of 128 columns
+  const int64_t whole = (ntiles / pairs) * pairs, rest = ntiles - whole;
+  const bool cut = rest > 0 && 2 * rest <= pairs;
+  const int items = (int)(cut ? whole + 2 * rest : ntiles), cut_from = cut ? (int)whole : 0x7fffffff;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * pairs));
   cfg.blockDim = dim3(kThreads);
@@ -513,7 +535,7 @@ int launch_typed(const int32_t* a, int64_t lda, const int32_t* b, int64_t ldb, c
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   QO_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_s4_unpack_kernel<OutT>, a_map, b_map, sa, sb, reinterpret_cast<OutT*>(out), acc_out,
-                                 reinterpret_cast<const OutT*>(bias), (int)t, (int)n, (int)k, status));
+                                 reinterpret_cast<const OutT*>(bias), (int)t, (int)n, (int)k, items, cut_from, status));
   return check_launch("gemm_s4_unpack_kernel");
 }
 
