@@ -163,6 +163,34 @@ def test_activation_scale_config_sampled_rows():
         assert np.all(np.abs(unpacked.astype(np.int32)).max(axis=1) >= 7)
 
 
+@pytest.mark.parametrize("tokens,feat", [(8192, 4096), (4096, 14336)])
+def test_full_size_every_row_follows_from_the_transform(tokens, feat):
+    """Full benchmark sizes, EVERY row: the scales and codes the tensor-core kernel stores are exactly what the reference's
+    elementwise steps (flatquant/ops.py:108-117: row extremes, clip, division by 7, quotient, round half to even, clamp)
+    give when applied, in bf16 like the reference, to the transformed activations the same kernel produces through its
+    transform-only entry point.  (The transform itself is compared with the oracle on sampled rows in the tests above;
+    rows are independent, so together the two cover every row at full size.)"""
+    m, n = O.get_decompose_dim(feat)
+    x, left, right = make_inputs(tokens, feat, "bf16", 20251, True)
+    xd, ld, rd = x.to(DEV), left.to(DEV), right.to(DEV)
+    codes, scales = abi_quantize(xd, ld, rd, 0.9, True, "bf16", policy=2)
+    assert lib.qo_last_quantizer_path() == 2
+    z = torch.empty(tokens, feat, device=DEV)
+    N.check(lib.qo_set_kernel_policy(2))
+    N.check(lib.qo_flatquant_transform(ptr(xd), feat, ptr(ld), ptr(rd), ptr(z), tokens, m, n, QD["bf16"], stream_ptr()))
+    lib.qo_set_kernel_policy(0)
+    assert lib.qo_device_status(stream_ptr()) == N.QO_OK
+    zb = z.bfloat16()
+    assert torch.equal(zb.float(), z)                                   # the entry point returns values of the activation dtype
+    xmax = torch.maximum((zb.amin(dim=1) * 0.9).abs(), zb.amax(dim=1) * 0.9)    # bf16 tensor times a Python float, as in the reference
+    want_s = (xmax / 7).clamp(min=1e-8)
+    assert torch.equal(scales, want_s.float())
+    want_q = torch.round(zb / want_s[:, None]).clamp(-8, 7).to(torch.int32)
+    sh = torch.arange(8, device=DEV, dtype=torch.int32) * 4
+    got_q = ((codes[:, :, None] >> sh) & 15).reshape(tokens, feat) - 8   # nibble i of word p = code[8p + i] + 8
+    assert torch.equal(got_q, want_q)
+
+
 def test_row_stride_and_scale_dtype():
     x, left, right = make_inputs(40, 4096, "bf16", 77, True)
     wide = torch.zeros(40, 4096 + 64, dtype=x.dtype)
