@@ -151,6 +151,15 @@ def test_gemm_on_quantizer_output_full_size(n_out):
     np.testing.assert_array_equal(t2f(out)[rows], ref)
     out2 = abi_int4_matmul(aq, wp.t(), sa * 2, swd, "fp16")
     np.testing.assert_allclose(t2f(out2), 2 * t2f(out), rtol=2e-3, atol=1e-6)
+    # EVERY accumulator and output of the full product: float32 sums of integer products below 2^24 are exact in any
+    # order, so a float32 matmul of the unpacked codes (no TF32) is an exact integer reference at full size
+    assert not torch.backends.cuda.matmul.allow_tf32
+    sh = torch.arange(8, device=DEV, dtype=torch.int32) * 4
+    a_codes = (((aq[:, :, None] >> sh) & 15) - 8).reshape(4096, 4096).float()
+    w_codes = (((wp[:, :, None] >> sh) & 15) - 8).reshape(n_out, 4096).float()
+    acc_all = a_codes @ w_codes.t()
+    assert torch.equal(acc.float(), acc_all)
+    assert torch.equal(out, ((acc_all * sa[:, None]) * swd[None, :]).half())
 
 
 @pytest.mark.parametrize("packed", [False, True])
