@@ -722,6 +722,51 @@ def stack_record(env: Env, args):
                   "bound": "NVLink: every GPU receives (N-1)/N of the 5.64 GB of outputs per step; the compute of the next projection hides under it",
                   "gpu_launches": glaunches, "clocks": gclocks})
         rec["with_gather"] = g
+
+        # The same gather done by the GEMM itself: its epilogue stores this rank's output rows into every rank's buffer
+        # (the peers' buffers are mapped into this process with CUDA IPC).  No collective kernel, nothing takes SMs
+        # from the GEMM.  The buffers of the NCCL variant above are reused as the destinations.
+        try:
+            for full in fulls:
+                full.fill_(0)
+            torch.cuda.synchronize()
+            env.barrier()
+            # (GatheredOutput allocates its own buffer; here the existing ones are shared instead)
+            dsts = [adopt_gathered(sharding, full, env) for full in fulls]
+
+            def step_fused(i, sp):
+                for layer, dst in zip(layers, dsts):
+                    name, k, n_out, m, n, left, right, wp, w8, sw = layer[:10]
+                    x = xin[k]
+                    arr = (C.c_void_p * env.world)(*dst.ptrs)
+                    for r0 in range(0, tloc, chunk):
+                        rows = min(chunk, tloc - r0)
+                        nat.check(lib.qo_w4a4_linear_gather(C.c_void_p(x.data_ptr() + r0 * k * 2), k, vp(left), vp(right), vp(wp), vp(sw), None,
+                                                            arr, env.world, start + r0, rows, m, n, n_out, CLIP, nat.QO_BF16, nat.QO_BF16,
+                                                            vp(ws), ws_need, sp))
+
+            fregions, flaunches, fclocks = time_regions(env, step_fused, steps, 2, max(3, min(args.sub_repeats, 5)))
+            f = summarize(fregions, steps)
+            fsec = f["ms_per_step"] / 1e3
+            torch.cuda.synchronize()
+            env.barrier()
+            fused_ok = True
+            for r in range(env.world):
+                s0, cnt = sharding.shard_rows(STACK_TOKENS, env.world, r)
+                mine = torch.stack([full[s0:s0 + cnt].view(torch.int16).to(torch.int64).sum() for full in fulls])
+                fused_ok = fused_ok and bool(torch.equal(mine, all_loc[r]))
+            fused_ok = fused_ok and bool(torch.equal(fulls[0][start:start + tloc], layers[0][10]))
+            f.update({"value": STACK_TOKENS / fsec, "unit": "tokens/s", "gathered_equals_local_slices": fused_ok,
+                      "bytes_sent_per_gpu": recv, "nvlink_GBps_per_gpu": recv / fsec / 1e9,
+                      "how": "qo_w4a4_linear_gather: the GEMM's epilogue stores its rows into every rank's buffer over NVLink (peer memory "
+                             "mapped with CUDA IPC); no collective kernel",
+                      "gpu_launches": flaunches, "clocks": fclocks})
+            rec["with_gather_fused"] = f
+            env.barrier()
+            for d in dsts:
+                d.close()
+        except Exception as e:  # the plain and the NCCL figures stand without it
+            rec["with_gather_fused"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
         del fulls
     else:
         rec["with_gather"] = {"skipped": "one rank: nothing to gather"}
@@ -731,6 +776,31 @@ def stack_record(env: Env, args):
     del layers, xin, ws
     torch.cuda.empty_cache()
     return rec
+
+
+def adopt_gathered(sharding, full, env):
+    """A sharding.GatheredOutput around an existing [total_rows, cols] buffer of this rank (every rank calls this in
+    the same order): the buffers are exported, exchanged and mapped exactly as GatheredOutput does for its own."""
+    import torch.distributed as dist
+
+    from quant_ops_b200 import _native as nat
+
+    d = sharding.GatheredOutput.__new__(sharding.GatheredOutput)
+    d.group, d.world, d.rank, d.full = None, env.world, env.rank, full
+    d.start, d.count = sharding.shard_rows(full.shape[0], env.world, env.rank)
+    handle = C.create_string_buffer(64)
+    offset = C.c_int64()
+    nat.check(nat.lib.qo_peer_export(C.c_void_p(full.data_ptr()), handle, C.byref(offset)))
+    everyone = [None] * env.world
+    dist.all_gather_object(everyone, (handle.raw, int(offset.value)))
+    d._handles, d.ptrs = [], []
+    for r, (h, off) in enumerate(everyone):
+        if r == env.rank:
+            d.ptrs.append(full.data_ptr())
+        else:
+            d.ptrs.append(sharding._open_peer(h) + off)
+            d._handles.append(h)
+    return d
 
 
 def cpu_stack(sample):

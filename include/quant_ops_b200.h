@@ -185,6 +185,36 @@ QO_API int qo_w4a4_linear(const void* x, int64_t ldx, const void* left, const vo
                           int out_dtype, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Fused layer whose outputs are ALL-GATHERED over the row-sharding ranks by the GEMM itself: rank r holds rows
+ * [row_offset, row_offset + tokens) of a layer input that is split by rows over the GPUs of one node, and the kernel's
+ * epilogue stores its output rows straight into every rank's copy of the gathered output (plain stores to peer memory
+ * over NVLink), this rank's own copy included.  No collective kernel runs and no SM is taken from the GEMM.
+ * The reference has no counterpart (it is single-GPU); this serves the optional output all-gather of a row-sharded
+ * deployment.  Only prefill-sized products take this route (at least 48 tiles of 256 x 256, k a multiple of 256, n_out
+ * a multiple of 16); anything else returns QO_ERR_UNSUPPORTED and the caller gathers with its collective library.
+ *
+ *   dsts        host array of n_dst (1 .. 8) device pointers to buffers [total_rows, n_out] in out_dtype, 32-byte aligned:
+ *               this GPU's own buffer and the peers' buffers as mapped into this process (qo_peer_open)
+ *   row_offset  first row of this rank's slice in those buffers
+ * The caller orders the ranks: a destination buffer may be read once every rank's call has completed on its stream
+ * (a barrier across the ranks after a stream synchronise), and must not be rewritten before every reader is done.
+ */
+QO_API int qo_w4a4_linear_gather(const void* x, int64_t ldx, const void* left, const void* right,
+                                 const int32_t* w_packed, const float* w_scale, const void* bias, void* const* dsts,
+                                 int n_dst, int64_t row_offset, int64_t tokens, int m, int n, int64_t n_out,
+                                 float clip_ratio, int in_dtype, int out_dtype, void* workspace, size_t workspace_bytes,
+                                 void* stream);
+/*
+ * Sharing a device buffer with the other processes of the node (CUDA IPC), for the destinations above.
+ * qo_peer_export: handle (64 bytes) of the allocation that contains ptr, and ptr's offset inside it.
+ * qo_peer_open:   maps an allocation exported by ANOTHER process into this one (peer access is enabled as needed);
+ *                 *base + offset is the exported pointer.  qo_peer_close unmaps it (after the last kernel using it).
+ */
+QO_API int qo_peer_export(const void* ptr, void* handle64, int64_t* offset);
+QO_API int qo_peer_open(const void* handle64, void** base);
+QO_API int qo_peer_close(void* base);
+
+/*
  * Layer form with weights prepared once.  The weights of a layer do not change between calls, so a host that can
  * spend about k bytes per output channel keeps them widened to int8 (qo_prepare_weights, at load time; the buffer is
  * opaque: the GEMM's own layout, blocks of 256 output channels x 128 values, padded to whole blocks) and the

@@ -36,6 +36,10 @@ PROTOTYPES = {
     "qo_int4_matmul_static": (_int, [_vp, _i64, _vp, _i64, _i64, _vp, _vp, _vp, _int, _i64, _i64, _i64, _vp]),
     "qo_w4a4_linear_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "qo_w4a4_linear": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _int, _int, _i64, _f32, _int, _int, _vp, _sz, _vp]),
+    "qo_w4a4_linear_gather": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, C.POINTER(_vp), _int, _i64, _i64, _int, _int, _i64, _f32, _int, _int, _vp, _sz, _vp]),
+    "qo_peer_export": (_int, [_vp, _vp, C.POINTER(_i64)]),
+    "qo_peer_open": (_int, [_vp, C.POINTER(_vp)]),
+    "qo_peer_close": (_int, [_vp]),
     "qo_prepared_weights_bytes": (_sz, [_i64, _i64]),
     "qo_prepare_weights": (_int, [_vp, _vp, _i64, _i64, _vp]),
     "qo_w4a4_linear_prepared_workspace_bytes": (_sz, [_i64, _i64, _i64]),

@@ -1,4 +1,6 @@
 // extern "C" entry points: argument validation, kernel selection, workspaces.  No kernels live here.
+#include <cuda.h>
+
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -332,6 +334,104 @@ int qo_w4a4_linear(const void* x, int64_t ldx, const void* left, const void* rig
   return int4_matmul_impl(a_packed, k / 8, w_packed, 1, k / 8, a_scale, w_scale, out, out_dtype, tokens, k, n_out,
                           nullptr, bias, ws + off_gemm, workspace_bytes - off_gemm,
                           reinterpret_cast<cudaStream_t>(stream), /*b_is_layer_weight=*/t_quant_path == 2);
+}
+
+int qo_w4a4_linear_gather(const void* x, int64_t ldx, const void* left, const void* right, const int32_t* w_packed,
+                          const float* w_scale, const void* bias, void* const* dsts, int n_dst, int64_t row_offset,
+                          int64_t tokens, int m, int n, int64_t n_out, float clip_ratio, int in_dtype, int out_dtype,
+                          void* workspace, size_t workspace_bytes, void* stream) {
+  clear_error();
+  const int64_t k = (int64_t)m * n;
+  if (m <= 0 || n <= 0 || k % 8) return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear_gather: m*n must be a positive multiple of 8");
+  if (out_dtype != QO_F16 && out_dtype != QO_BF16) return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear_gather: out_dtype must be QO_F16 or QO_BF16");
+  if (tokens < 0 || n_out < 0 || row_offset < 0) return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear_gather: negative size or offset");
+  if (n_dst < 1 || n_dst > 8 || !dsts) return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear_gather: 1 .. 8 destinations");
+  if (tokens == 0 || n_out == 0) return QO_OK;
+  if (!x || !left || !right || !w_packed || !w_scale) return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear_gather: null pointer argument");
+  int dev = 0, rc = require_device(&dev);
+  if (rc) return rc;
+  const size_t need = qo_w4a4_linear_workspace_bytes(tokens, k, n_out);
+  if (workspace == nullptr) {
+    if ((rc = scratch_get(g_scratch, dev, need, &workspace))) return rc;
+    workspace_bytes = need;
+  }
+  if (workspace_bytes < need) return fail(QO_ERR_WORKSPACE, "w4a4_linear_gather: workspace of %zu bytes, need %zu", workspace_bytes, need);
+  if (t_policy == 1 || !gemm_unpack_preferred(tokens, k, n_out) ||
+      !gemm_unpack_supported(tokens, k, n_out, workspace, k / 8, w_packed, 1, k / 8) || n_out % 16)
+    return fail(QO_ERR_UNSUPPORTED, "w4a4_linear_gather: only prefill-sized products gather in the kernel (tokens=%lld k=%lld n_out=%lld)",
+                (long long)tokens, (long long)k, (long long)n_out);
+  GatherDsts g = {};
+  g.n_dst = n_dst;
+  g.row_offset = row_offset;
+  for (int d = 0; d < n_dst; ++d) g.ptr[d] = dsts[d];
+  char* ws = reinterpret_cast<char*>(workspace);
+  int32_t* a_packed = reinterpret_cast<int32_t*>(ws);
+  const size_t off_scale = align_up((size_t)tokens * (size_t)(k / 8) * 4, 256);
+  float* a_scale = reinterpret_cast<float*>(ws + off_scale);
+  rc = qo_flatquant_quantize(x, ldx, left, right, a_packed, a_scale, tokens, m, n, clip_ratio, in_dtype, 1, QO_F32, stream);
+  if (rc) return rc;
+  uint32_t* status = device_status_word(dev);
+  if (!status) return fail(QO_ERR_CUDA, "w4a4_linear_gather: could not allocate the device status word");
+  t_gemm_path = 2;
+  rc = launch_gemm_unpack(a_packed, k / 8, w_packed, k / 8, a_scale, w_scale, nullptr, out_dtype, tokens, k, n_out, nullptr, bias,
+                          status, reinterpret_cast<cudaStream_t>(stream), &g);
+  if (rc == QO_ERR_UNSUPPORTED && qo_last_error()[0] == 0)
+    return fail(QO_ERR_UNSUPPORTED, "w4a4_linear_gather: this device cannot co-schedule the CTA pairs of the kernel");
+  return rc;
+}
+
+// ---- sharing device buffers between the processes of a node (CUDA IPC) -------------------------------------------------
+namespace {
+typedef CUresult (*PointerGetAttributeFn)(void*, CUpointer_attribute, CUdeviceptr);
+PointerGetAttributeFn pointer_attribute_fn() {
+  static PointerGetAttributeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuPointerGetAttribute", &p, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PointerGetAttributeFn>(p);
+    else
+      (void)cudaGetLastError();
+  });
+  return fn;
+}
+}  // namespace
+
+int qo_peer_export(const void* ptr, void* handle64, int64_t* offset) {
+  clear_error();
+  if (!ptr || !handle64 || !offset) return fail(QO_ERR_INVALID_ARGUMENT, "peer_export: null pointer argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  int rc = require_device(nullptr);
+  if (rc) return rc;
+  PointerGetAttributeFn attr = pointer_attribute_fn();
+  if (!attr) return fail(QO_ERR_CUDA, "peer_export: cuPointerGetAttribute is not available");
+  CUdeviceptr base = 0;
+  const CUresult r = attr(&base, CU_POINTER_ATTRIBUTE_RANGE_START_ADDR, reinterpret_cast<CUdeviceptr>(ptr));
+  if (r != CUDA_SUCCESS || base == 0) return fail(QO_ERR_CUDA, "peer_export: not a device allocation (driver code %d)", (int)r);
+  cudaIpcMemHandle_t h;
+  QO_CUDA_TRY(cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base)));
+  memcpy(handle64, &h, sizeof(h));
+  *offset = (int64_t)(reinterpret_cast<CUdeviceptr>(ptr) - base);
+  return QO_OK;
+}
+
+int qo_peer_open(const void* handle64, void** base) {
+  clear_error();
+  if (!handle64 || !base) return fail(QO_ERR_INVALID_ARGUMENT, "peer_open: null pointer argument");
+  int rc = require_device(nullptr);
+  if (rc) return rc;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  QO_CUDA_TRY(cudaIpcOpenMemHandle(base, h, cudaIpcMemLazyEnablePeerAccess));
+  return QO_OK;
+}
+
+int qo_peer_close(void* base) {
+  clear_error();
+  if (!base) return QO_OK;
+  QO_CUDA_TRY(cudaIpcCloseMemHandle(base));
+  return QO_OK;
 }
 
 size_t qo_prepared_weights_bytes(int64_t n_out, int64_t k) {

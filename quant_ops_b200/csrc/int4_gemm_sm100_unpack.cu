@@ -153,12 +153,15 @@ __device__ __forceinline__ bool issue_stage(uint32_t d_tmem, uint32_t a_tmem, ui
   return ok != 0;
 }
 
-template <typename OutT>
+// GATHER: the outputs are not stored to `out` but, at row `row_offset + row`, into every buffer of `dsts` -- this GPU's
+// own copy of the gathered output and the peers' copies, mapped into this process (plain stores over NVLink; the
+// all-gather of a row-sharded layer's outputs costs no kernel of its own and no SMs).
+template <typename OutT, bool GATHER>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_s4_unpack_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
                       const float* __restrict__ sa, const float* __restrict__ sb, OutT* __restrict__ out,
                       int32_t* __restrict__ acc_out, const OutT* __restrict__ bias, int t, int n, int k, int items, int cut_from,
-                      uint32_t* __restrict__ status) {
+                      uint32_t* __restrict__ status, const __grid_constant__ GatherDsts dsts) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Bars* bars = reinterpret_cast<Bars*>(smem + kOffBar);
@@ -293,7 +296,7 @@ gemm_s4_unpack_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_co
         }
         const int col0 = colw + cc;
         if (row_ok && col0 < n) {
-          OutT* orow = out + (int64_t)row * n + col0;
+          const int64_t off = (int64_t)(GATHER ? row + dsts.row_offset : row) * n + col0;
           // 16 columns at a time: eight packed words live beside the 32 accumulators, not sixteen
 #pragma unroll
           for (int jh = 0; jh < 2; ++jh) {
@@ -318,12 +321,17 @@ gemm_s4_unpack_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_co
             }
             // A lane owns a row, so a warp's store instruction touches 32 different lines; the exposed part of the
             // epilogue is bound by those line accesses.  32-byte stores (whole sectors) halve their number.
-            if (wide_stores) {
-              asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(orow + 16 * jh), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+            if (GATHER) {
+              // (the host admits only row lengths and buffers that make every piece a whole 32-byte sector)
+              for (int d = 0; d < dsts.n_dst; ++d)
+                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(reinterpret_cast<OutT*>(dsts.ptr[d]) + off + 16 * jh),
+                             "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+            } else if (wide_stores) {
+              asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(out + off + 16 * jh), "r"(w[0]), "r"(w[1]), "r"(w[2]),
                            "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
             } else {
-              reinterpret_cast<uint4*>(orow + 16 * jh)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-              if (col0 + 16 * jh + 8 < n) reinterpret_cast<uint4*>(orow + 16 * jh)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+              reinterpret_cast<uint4*>(out + off + 16 * jh)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+              if (col0 + 16 * jh + 8 < n) reinterpret_cast<uint4*>(out + off + 16 * jh)[1] = make_uint4(w[4], w[5], w[6], w[7]);
             }
           }
           if (acc_out != nullptr) {
@@ -478,12 +486,12 @@ int make_map_packed(CUtensorMap* map, const void* base, int64_t rows, int64_t k,
 }
 
 // CTA pairs of this kernel the device runs at once (0 if the query fails); cached per device
-template <typename OutT>
+template <typename OutT, bool GATHER>
 int max_pairs(int dev) {
   static int cached[64] = {};
   int& c = cached[dev & 63];
   if (c == 0) {
-    auto kern = gemm_s4_unpack_kernel<OutT>;
+    auto kern = gemm_s4_unpack_kernel<OutT, GATHER>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) { (void)cudaGetLastError(); c = -1; return 0; }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * 74);
@@ -503,12 +511,13 @@ int max_pairs(int dev) {
   return c > 0 ? c : 0;
 }
 
-template <typename OutT>
+template <typename OutT, bool GATHER>
 int launch_typed(const int32_t* a, int64_t lda, const int32_t* b, int64_t ldb, const float* sa, const float* sb, void* out,
-                 int32_t* acc_out, const void* bias, int64_t t, int64_t k, int64_t n, uint32_t* status, cudaStream_t stream) {
+                 int32_t* acc_out, const void* bias, int64_t t, int64_t k, int64_t n, uint32_t* status, const GatherDsts& dsts,
+                 cudaStream_t stream) {
   int dev = 0;
   QO_CUDA_TRY(cudaGetDevice(&dev));
-  const int pairs_max = max_pairs<OutT>(dev);
+  const int pairs_max = max_pairs<OutT, GATHER>(dev);
   if (pairs_max <= 0) return QO_ERR_UNSUPPORTED;
   CUtensorMap a_map, b_map;
   int rc = make_map_packed(&a_map, a, t, k, lda, kBM);
@@ -534,8 +543,8 @@ int launch_typed(const int32_t* a, int64_t lda, const int32_t* b, int64_t ldb, c
   attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  QO_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_s4_unpack_kernel<OutT>, a_map, b_map, sa, sb, reinterpret_cast<OutT*>(out), acc_out,
-                                 reinterpret_cast<const OutT*>(bias), (int)t, (int)n, (int)k, items, cut_from, status));
+  QO_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_s4_unpack_kernel<OutT, GATHER>, a_map, b_map, sa, sb, reinterpret_cast<OutT*>(out), acc_out,
+                                 reinterpret_cast<const OutT*>(bias), (int)t, (int)n, (int)k, items, cut_from, status, dsts));
   return check_launch("gemm_s4_unpack_kernel");
 }
 
@@ -565,13 +574,22 @@ bool gemm_unpack_preferred(int64_t t, int64_t k, int64_t n) {
 // returns QO_ERR_UNSUPPORTED without a message when the device cannot co-schedule CTA pairs of this kernel
 int launch_gemm_unpack(const int32_t* a, int64_t lda, const int32_t* b, int64_t ldb, const float* sa, const float* sb, void* out,
                        int out_dtype, int64_t t, int64_t k, int64_t n, int32_t* acc_out, const void* bias, uint32_t* status,
-                       cudaStream_t stream) {
-  if (reinterpret_cast<uintptr_t>(out) % 16 || (acc_out && reinterpret_cast<uintptr_t>(acc_out) % 16) ||
-      (bias && reinterpret_cast<uintptr_t>(bias) % 4))
+                       cudaStream_t stream, const GatherDsts* gather) {
+  if (out_dtype != QO_F16 && out_dtype != QO_BF16) return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: out_dtype must be QO_F16 or QO_BF16");
+  if (bias && reinterpret_cast<uintptr_t>(bias) % 4) return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: bias must be 4-byte aligned");
+  if (gather != nullptr) {
+    if (n % 16) return fail(QO_ERR_UNSUPPORTED, "w4a4_linear_gather: n_out must be a multiple of 16");
+    for (int d = 0; d < gather->n_dst; ++d)
+      if (!gather->ptr[d] || reinterpret_cast<uintptr_t>(gather->ptr[d]) % 32)
+        return fail(QO_ERR_INVALID_ARGUMENT, "w4a4_linear_gather: destination %d is null or not 32-byte aligned", d);
+    if (out_dtype == QO_F16) return launch_typed<__half, true>(a, lda, b, ldb, sa, sb, nullptr, nullptr, bias, t, k, n, status, *gather, stream);
+    return launch_typed<__nv_bfloat16, true>(a, lda, b, ldb, sa, sb, nullptr, nullptr, bias, t, k, n, status, *gather, stream);
+  }
+  if (reinterpret_cast<uintptr_t>(out) % 16 || (acc_out && reinterpret_cast<uintptr_t>(acc_out) % 16))
     return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: outputs of the tcgen05 kernel must be 16-byte aligned");
-  if (out_dtype == QO_F16) return launch_typed<__half>(a, lda, b, ldb, sa, sb, out, acc_out, bias, t, k, n, status, stream);
-  if (out_dtype == QO_BF16) return launch_typed<__nv_bfloat16>(a, lda, b, ldb, sa, sb, out, acc_out, bias, t, k, n, status, stream);
-  return fail(QO_ERR_INVALID_ARGUMENT, "int4_matmul: out_dtype must be QO_F16 or QO_BF16");
+  const GatherDsts none = {};
+  if (out_dtype == QO_F16) return launch_typed<__half, false>(a, lda, b, ldb, sa, sb, out, acc_out, bias, t, k, n, status, none, stream);
+  return launch_typed<__nv_bfloat16, false>(a, lda, b, ldb, sa, sb, out, acc_out, bias, t, k, n, status, none, stream);
 }
 
 }  // namespace qo

@@ -186,9 +186,16 @@ int launch_gemm_sm100_pair(const int8_t* a8, const int8_t* b8, const float* sa, 
 // packed-int4 GEMM that unpacks inside the kernel (int4_gemm_sm100_unpack.cu): b is [n, k/8] with row stride ldb words
 bool gemm_unpack_supported(int64_t t, int64_t k, int64_t n, const void* a, int64_t lda, const void* b, int64_t bsk, int64_t bsn);
 bool gemm_unpack_preferred(int64_t t, int64_t k, int64_t n);
+// destinations of the fused all-gather (see gemm_s4_unpack_kernel): the buffers [total_rows, n] of this GPU and its
+// peers; this rank's rows start at row_offset
+struct GatherDsts {
+  void* ptr[8];
+  int n_dst;
+  long long row_offset;
+};
 int launch_gemm_unpack(const int32_t* a, int64_t lda, const int32_t* b, int64_t ldb, const float* sa, const float* sb, void* out,
                        int out_dtype, int64_t t, int64_t k, int64_t n, int32_t* acc_out, const void* bias, uint32_t* status,
-                       cudaStream_t stream);
+                       cudaStream_t stream, const GatherDsts* gather = nullptr);
 
 // pieces of the tcgen05 GEMM, used separately by the fused layer
 int launch_widen_rows(const int32_t* in, int64_t ld_words, int8_t* out, int64_t rows, int64_t k, cudaStream_t stream, bool blocked,

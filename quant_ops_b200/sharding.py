@@ -3,7 +3,8 @@
 Every stage of the path is independent per token row (reference: src/quant_ops/ops/quantization/flatquant/ops.py:100-117,
 cuda_int4_matmul_kernel.cu:114-116), so the tokens are split contiguously over one process per GPU and the int4
 weights, weight scales, L and R are replicated.  Nothing on the data path communicates; `all_gather_rows` exists for
-callers that need every rank to hold the full output afterwards.
+callers that need every rank to hold the full output afterwards; `GatheredOutput` + `w4a4_linear_gather` do the same
+without a collective: the GEMM's epilogue stores its rows into every rank's buffer over NVLink.
 """
 from __future__ import annotations
 
@@ -64,3 +65,104 @@ def sharded_apply(fn: Callable[[torch.Tensor], torch.Tensor], x_full_rows: int, 
     """Runs `fn` (e.g. a W4A4Linear) on this rank's rows; optionally gathers the outputs of all ranks."""
     y = fn(x_local)
     return all_gather_rows(y, x_full_rows, group) if gather else y
+
+
+# ---- all-gather fused into the layer's GEMM (one node, CUDA IPC) --------------------------------------------------------
+_opened: dict = {}  # exported allocation (handle bytes) -> [base address in this process, users]
+
+
+def _open_peer(handle: bytes) -> int:
+    import ctypes as C
+
+    from . import _native as nat
+
+    entry = _opened.get(handle)
+    if entry is None:
+        base = C.c_void_p()
+        nat.check(nat.lib.qo_peer_open(C.c_char_p(handle), C.byref(base)))
+        entry = _opened[handle] = [base.value, 0]
+    entry[1] += 1
+    return entry[0]
+
+
+def _close_peer(handle: bytes) -> None:
+    import ctypes as C
+
+    from . import _native as nat
+
+    entry = _opened.get(handle)
+    if entry is None:
+        return
+    entry[1] -= 1
+    if entry[1] == 0:
+        del _opened[handle]
+        nat.check(nat.lib.qo_peer_close(C.c_void_p(entry[0])))
+
+
+class GatheredOutput:
+    """A layer output [total_rows, cols] that every rank of the group holds in full and that the ranks fill for one
+    another: `full` is this rank's buffer, `ptrs[r]` is rank r's buffer as seen from this process.  Ranks are the
+    processes of ONE node (CUDA IPC).  `close()` unmaps the peers' buffers; call it on every rank, after a barrier that
+    follows the last kernel writing them, and before the buffers are freed."""
+
+    def __init__(self, total_rows: int, cols: int, dtype: torch.dtype, device: Optional[torch.device] = None,
+                 group: Optional[dist.ProcessGroup] = None):
+        import ctypes as C
+
+        from . import _native as nat
+
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks (one node)")
+        self.full = torch.empty(total_rows, cols, dtype=dtype, device=device if device is not None else torch.cuda.current_device())
+        self.start, self.count = shard_rows(total_rows, self.world, self.rank)
+        handle = C.create_string_buffer(64)
+        offset = C.c_int64()
+        nat.check(nat.lib.qo_peer_export(C.c_void_p(self.full.data_ptr()), handle, C.byref(offset)))
+        mine = (handle.raw, int(offset.value))
+        everyone: list = [None] * self.world
+        dist.all_gather_object(everyone, mine, group=group)
+        self._handles: List[bytes] = []
+        self.ptrs: List[int] = []
+        for r, (h, off) in enumerate(everyone):
+            if r == self.rank:
+                self.ptrs.append(self.full.data_ptr())
+            else:
+                self.ptrs.append(_open_peer(h) + off)
+                self._handles.append(h)
+
+    def close(self) -> None:
+        for h in self._handles:
+            _close_peer(h)
+        self._handles = []
+
+
+def w4a4_linear_gather(x_local: torch.Tensor, left_trans: torch.Tensor, right_trans: torch.Tensor, w_packed: torch.Tensor,
+                       w_scale: torch.Tensor, dst: GatheredOutput, bias: Optional[torch.Tensor] = None,
+                       clip_ratio: float = 1.0, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The fused layer on this rank's rows, its outputs stored by the GEMM into every rank's `dst` buffer (rows
+    dst.start .. dst.start + dst.count).  Returns dst.full, whose other rows the other ranks fill: it is complete after
+    every rank's call has finished and the ranks have met (a stream synchronise, then a barrier).  Raises for shapes the
+    fused kernel does not take (small token counts): gather those with all_gather_rows."""
+    import ctypes as C
+
+    from . import _native as nat
+
+    tokens, k = x_local.shape
+    if tokens != dst.count:
+        raise ValueError(f"this rank holds {tokens} rows, its shard has {dst.count}")
+    m, n = left_trans.shape[0], right_trans.shape[0]
+    n_out = w_packed.shape[0]
+    if tuple(dst.full.shape[1:]) != (n_out,) or dst.full.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("dst must be [total_rows, n_out] in float16 or bfloat16")
+    qd = {torch.float16: nat.QO_F16, torch.bfloat16: nat.QO_BF16, torch.float32: nat.QO_F32}
+    ptrs = (C.c_void_p * dst.world)(*dst.ptrs)
+    ws_ptr, ws_bytes = (None, 0) if workspace is None else (C.c_void_p(workspace.data_ptr()), workspace.numel() * workspace.element_size())
+    stream = C.c_void_p(torch.cuda.current_stream(x_local.device).cuda_stream)
+    nat.check(nat.lib.qo_w4a4_linear_gather(
+        C.c_void_p(x_local.data_ptr()), x_local.stride(0), C.c_void_p(left_trans.data_ptr()), C.c_void_p(right_trans.data_ptr()),
+        C.c_void_p(w_packed.data_ptr()), C.c_void_p(w_scale.data_ptr()), None if bias is None else C.c_void_p(bias.data_ptr()),
+        ptrs, dst.world, dst.start, tokens, m, n, n_out, float(clip_ratio), qd[x_local.dtype], qd[dst.full.dtype],
+        ws_ptr, ws_bytes, stream))
+    return dst.full

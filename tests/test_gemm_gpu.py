@@ -1,4 +1,6 @@
 """GPU parity of the packed-int4 GEMM, dequantize, pack/unpack, weight quantizer and the fused layer (C ABI)."""
+import ctypes as C
+
 import numpy as np
 import pytest
 import torch
@@ -283,6 +285,33 @@ def test_fused_layer_down_proj_shape(tokens):
     assert torch.equal(out, two_call)
     exact = O.round_to(O.int4_matmul(aq.cpu().numpy()[rows], wp.T, t2f(sa)[rows], sw, "bf16") + t2f(bias)[None, :], "bf16")
     np.testing.assert_array_equal(got[rows], exact)
+
+
+@pytest.mark.parametrize("n_out", [4096, 1024 + 4096])
+def test_gather_variant_writes_this_ranks_rows_into_every_destination(n_out):
+    """qo_w4a4_linear_gather with two destination buffers on this GPU standing in for two ranks' buffers: rows
+    row_offset .. row_offset + tokens of BOTH hold the bits of the plain fused layer, every other row is untouched.
+    (Mapping another process's buffer is exercised by the multi-GPU benchmark; the kernel sees plain pointers.)"""
+    tokens, k, total, row_offset = 2048, 4096, 5000, 1111
+    x, left, right = make_inputs(tokens, k, "bf16", 20270, True)
+    g = torch.Generator().manual_seed(20271)
+    wq, sw = O.quantize_weights((torch.randn(n_out, k, generator=g) * 0.02).numpy())
+    wpd, swd = torch.from_numpy(O.pack_int4_to_int32(wq)).to(DEV), torch.from_numpy(sw).to(DEV)
+    bias = (torch.randn(n_out, generator=g) * 0.1).bfloat16().to(DEV)
+    xd, ld, rd = x.to(DEV), left.to(DEV), right.to(DEV)
+    want = abi_linear(xd, ld, rd, wpd, swd, bias, 0.9, "bf16", "bf16")
+    dsts = [torch.full((total, n_out), -7.0, dtype=torch.bfloat16, device=DEV) for _ in range(2)]
+    arr = (C.c_void_p * 2)(*[d.data_ptr() for d in dsts])
+    N.check(lib.qo_w4a4_linear_gather(ptr(xd), xd.stride(0), ptr(ld), ptr(rd), ptr(wpd), ptr(swd), ptr(bias), arr, 2, row_offset, tokens,
+                                      left.shape[0], right.shape[0], n_out, 0.9, QD["bf16"], QD["bf16"], None, 0, stream_ptr()))
+    assert lib.qo_device_status(stream_ptr()) == N.QO_OK, lib.qo_last_error()
+    for d in dsts:
+        assert torch.equal(d[row_offset:row_offset + tokens], want)
+        assert bool((d[:row_offset] == -7.0).all()) and bool((d[row_offset + tokens:] == -7.0).all())
+    # a decode-sized call has no fused gather: the caller is told, nothing is written
+    rc = lib.qo_w4a4_linear_gather(ptr(xd), xd.stride(0), ptr(ld), ptr(rd), ptr(wpd), ptr(swd), ptr(bias), arr, 2, 0, 16,
+                                   left.shape[0], right.shape[0], n_out, 0.9, QD["bf16"], QD["bf16"], None, 0, stream_ptr())
+    assert rc == N.QO_ERR_UNSUPPORTED and b"prefill" in lib.qo_last_error()
 
 
 def abi_linear_prepared(x, left, right, wp, w8, sw, bias, clip, dtype, out_dtype):
