@@ -641,8 +641,10 @@ def stack_record(env: Env, args):
         layers.append((name, k, n_out, m, n, left.to(env.dev), right.to(env.dev), wp, w8, sw, out, left, right))
     ws = torch.empty(ws_need, dtype=torch.uint8, device=env.dev)
 
-    def run_layer(layer, sp):
+    def run_layer(layer, sp, out_override=None):
         name, k, n_out, m, n, left, right, wp, w8, sw, out = layer[:11]
+        if out_override is not None:
+            out = out_override
         x = xin[k]
         for r0 in range(0, tloc, chunk):
             rows = min(chunk, tloc - r0)
@@ -762,6 +764,40 @@ def stack_record(env: Env, args):
                              "mapped with CUDA IPC); no collective kernel",
                       "gpu_launches": flaunches, "clocks": fclocks})
             rec["with_gather_fused"] = f
+            env.barrier()
+
+            # Third variant: the plain layer, then copy-engine transfers of its output rows into every rank's buffer on a
+            # side stream (no SM is used), under the next projection's kernels.
+            for full in fulls:
+                full.fill_(0)
+            torch.cuda.synchronize()
+            env.barrier()
+
+            def step_push(i, sp):
+                for layer, dst in zip(layers, dsts):
+                    run_layer(layer, sp, dst.local_rows())  # the layer writes this rank's rows of its own gathered buffer
+                    done = torch.cuda.Event()
+                    done.record(env.stream)
+                    comm.wait_event(done)
+                    dst.push_rows(dst.local_rows(), start, comm, include_self=False)
+                env.stream.wait_stream(comm)
+
+            pregions, plaunches, pclocks = time_regions(env, step_push, steps, 2, max(3, min(args.sub_repeats, 5)))
+            pr = summarize(pregions, steps)
+            psec = pr["ms_per_step"] / 1e3
+            torch.cuda.synchronize()
+            env.barrier()
+            push_ok = True
+            for r in range(env.world):
+                s0, cnt = sharding.shard_rows(STACK_TOKENS, env.world, r)
+                mine = torch.stack([full[s0:s0 + cnt].view(torch.int16).to(torch.int64).sum() for full in fulls])
+                push_ok = push_ok and bool(torch.equal(mine, all_loc[r]))
+            pr.update({"value": STACK_TOKENS / psec, "unit": "tokens/s", "gathered_equals_local_slices": push_ok,
+                       "bytes_sent_per_gpu": recv, "nvlink_GBps_per_gpu": recv / psec / 1e9,
+                       "how": "the layer writes its rows of its own gathered buffer; GatheredOutput.push_rows sends them into the peers' "
+                              "buffers (CUDA IPC) with copy-engine transfers on a side stream, under the next projection's kernels",
+                       "gpu_launches": plaunches, "clocks": pclocks})
+            rec["with_gather_copy_engine"] = pr
             env.barrier()
             for d in dsts:
                 d.close()

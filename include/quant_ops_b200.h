@@ -213,6 +213,9 @@ QO_API int qo_w4a4_linear_gather(const void* x, int64_t ldx, const void* left, c
 QO_API int qo_peer_export(const void* ptr, void* handle64, int64_t* offset);
 QO_API int qo_peer_open(const void* handle64, void** base);
 QO_API int qo_peer_close(void* base);
+/* bytes from this GPU's memory into a mapped peer buffer (or any device buffer) on `stream`: a copy-engine transfer that
+ * takes no SM, for gathers that should run beside the kernels of another stream */
+QO_API int qo_peer_copy(void* dst, const void* src, size_t bytes, void* stream);
 
 /*
  * Layer form with weights prepared once.  The weights of a layer do not change between calls, so a host that can

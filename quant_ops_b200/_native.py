@@ -40,6 +40,7 @@ PROTOTYPES = {
     "qo_peer_export": (_int, [_vp, _vp, C.POINTER(_i64)]),
     "qo_peer_open": (_int, [_vp, C.POINTER(_vp)]),
     "qo_peer_close": (_int, [_vp]),
+    "qo_peer_copy": (_int, [_vp, _vp, _sz, _vp]),
     "qo_prepared_weights_bytes": (_sz, [_i64, _i64]),
     "qo_prepare_weights": (_int, [_vp, _vp, _i64, _i64, _vp]),
     "qo_w4a4_linear_prepared_workspace_bytes": (_sz, [_i64, _i64, _i64]),

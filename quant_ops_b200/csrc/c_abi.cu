@@ -434,6 +434,14 @@ int qo_peer_close(void* base) {
   return QO_OK;
 }
 
+int qo_peer_copy(void* dst, const void* src, size_t bytes, void* stream) {
+  clear_error();
+  if (bytes == 0) return QO_OK;
+  if (!dst || !src) return fail(QO_ERR_INVALID_ARGUMENT, "peer_copy: null pointer argument");
+  QO_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, reinterpret_cast<cudaStream_t>(stream)));
+  return QO_OK;
+}
+
 size_t qo_prepared_weights_bytes(int64_t n_out, int64_t k) {
   if (n_out <= 0 || k <= 0) return 0;
   return gemm_b8_bytes(n_out, k);

@@ -137,6 +137,29 @@ class GatheredOutput:
             _close_peer(h)
         self._handles = []
 
+    def local_rows(self) -> torch.Tensor:
+        """This rank's rows of its own buffer: a layer that writes its output here needs no local copy afterwards."""
+        return self.full[self.start:self.start + self.count]
+
+    def push_rows(self, local: torch.Tensor, first_row: int, stream: Optional[torch.cuda.Stream] = None,
+                  include_self: bool = True) -> None:
+        """Copies `local` ([rows, cols], rows first_row .. of the gathered output, contiguous) into every rank's buffer
+        (this rank's too unless include_self is False, e.g. when `local` already is a view of local_rows()) with
+        copy-engine transfers on `stream` (default: the current stream): they take no SM, so on a side stream they run
+        beside the next layer's kernels at the NVLink rate."""
+        import ctypes as C
+
+        from . import _native as nat
+
+        if not local.is_contiguous() or tuple(local.shape[1:]) != tuple(self.full.shape[1:]) or local.dtype != self.full.dtype:
+            raise ValueError("local must be a contiguous [rows, cols] tensor of the gathered output's dtype")
+        sp = C.c_void_p((stream or torch.cuda.current_stream(local.device)).cuda_stream)
+        row_bytes = self.full.stride(0) * self.full.element_size()
+        nbytes = local.shape[0] * row_bytes
+        for r in range(self.world if include_self else self.world - 1):  # peers first, each rank starting at its neighbour
+            order = (self.rank + 1 + r) % self.world
+            nat.check(nat.lib.qo_peer_copy(C.c_void_p(self.ptrs[order] + first_row * row_bytes), C.c_void_p(local.data_ptr()), nbytes, sp))
+
 
 def w4a4_linear_gather(x_local: torch.Tensor, left_trans: torch.Tensor, right_trans: torch.Tensor, w_packed: torch.Tensor,
                        w_scale: torch.Tensor, dst: GatheredOutput, bias: Optional[torch.Tensor] = None,
