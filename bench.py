@@ -397,6 +397,46 @@ def cpu_quantize(tokens, m, n, runs):
             "sample": f"all {tokens} tokens per step, min of {runs} steps; the reference's torch CPU op chain, {host_cores()} threads"}
 
 
+def dequantize_record(env: Env, args, tokens=TOKENS, feat=M * N_):
+    """dequantize_int4 of packed codes: [tokens, feat / 8] int32 + float32 scales -> float32 [tokens, feat] (write-bound)."""
+    torch, lib, nat = env.torch, env.lib, env.nat
+    g = torch.Generator(device=env.dev).manual_seed(SEED + 7)
+    nsets = 3  # 3 x (17 MB in + 134 MB out) > L2
+    codes = [torch.randint(-2**31, 2**31 - 1, (tokens, feat // 8), generator=g, device=env.dev, dtype=torch.int32) for _ in range(nsets)]
+    scales = [torch.rand(tokens, generator=g, device=env.dev) * 0.1 + 0.01 for _ in range(nsets)]
+    outs = [torch.empty(tokens, feat, device=env.dev) for _ in range(nsets)]
+    algo = tokens * (feat // 2 + 4 + 4 * feat)
+
+    def step(i, sp):
+        j = i % nsets
+        nat.check(lib.qo_dequantize_int4(vp(codes[j]), vp(scales[j]), vp(outs[j]), tokens, feat, 1, nat.QO_F32, sp))
+
+    regions, launches, clocks = time_regions(env, step, args.sub_steps, 3, args.sub_repeats)
+    rec = summarize(regions, args.sub_steps)
+    from oracle import w4a4_oracle as O
+
+    step(0, env.sp)
+    torch.cuda.synchronize()
+    rows = [0, 1, tokens // 2, tokens - 1]
+    ref = O.dequantize_int4(codes[0][rows].cpu().numpy(), scales[0][rows].cpu().numpy(), True)
+    parity_ok = bool((outs[0][rows].cpu().numpy() == ref).all())
+    gbps = algo / (rec["ms_per_step"] / 1e3) / 1e9
+    rec.update({"workload": f"dequantize_int4: packed codes [{tokens}, {feat // 8}] + scales -> float32 [{tokens}, {feat}]",
+                "value": gbps, "unit": "GB/s", "parity_vs_oracle_sample": parity_ok, "l2": f"{nsets} buffer sets ({nsets * algo // 10**6} MB) > L2",
+                "roofline": {"bound": "hbm", "achieved": gbps, "peak": env.hbm_peak, "unit": "GB/s", "frac": gbps / env.hbm_peak, "traffic": None,
+                             "peak_source": env.hbm_src, "algorithmic_bytes_per_launch": algo},
+                "gpu_launches": launches, "clocks": clocks})
+    if not args.no_cpu_baseline:
+        sample = 1024
+        c_cpu, s_cpu = codes[0][:sample].cpu().numpy(), scales[0][:sample].cpu().numpy()
+        sec = cpu_time(lambda: O.dequantize_int4(c_cpu, s_cpu, True), 1, 3)
+        rec["cpu_baseline"] = {"value": sample * (feat // 2 + 4 + 4 * feat) / sec / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+                               "ms_per_step": sec * 1e3, "sample": f"{sample} of the {tokens} tokens, min of 3; numpy restatement of the reference's unpack-and-scale loop"}
+    del codes, scales, outs
+    torch.cuda.empty_cache()
+    return rec
+
+
 # ---------------------------------------------------------------------------------------------------------------
 # GEMM
 # ---------------------------------------------------------------------------------------------------------------
@@ -893,6 +933,7 @@ def run_ours(args):
         if wl == "all":
             if env.world == 1:
                 line["quantize_wide"] = quantizer_record(env, _sub(args), 4096, 112, 128, "quantize_wide")
+                line["dequantize"] = dequantize_record(env, args)
                 line["gemm"] = gemm_records(env, args, [4096, 11008, 14336])
                 line["linear"] = linear_records(env, args, [1, 16, 256, 4096], [False, True])
             line["stack"] = stack_record(env, args)
