@@ -11,27 +11,31 @@ constexpr int kThreads = 256;
 // packed: one thread per half word -> 4 floats, so that consecutive lanes write consecutive 16-byte pieces (a warp's
 // store covers 512 contiguous bytes); four items per thread are in flight.  The output is 8x the input: the kernel is
 // bound by HBM writes.
+// Idx: 32-bit indices when the piece count allows (the usual case): the row of a piece is a division, and the 64-bit one
+// costs more instructions than the rest of the loop body together.
+template <typename Idx>
 __global__ void __launch_bounds__(kThreads)
 dequant_packed_kernel(const uint32_t* __restrict__ words, const void* __restrict__ scales, float* __restrict__ out,
-                      int64_t tokens, int64_t words_per_row, int scale_dtype) {
+                      int64_t tokens, int64_t words_per_row_arg, int scale_dtype) {
   constexpr int kUnroll = 4;
-  const int64_t total = tokens * words_per_row * 2;  // 16-byte output pieces
-  const int64_t stride = (int64_t)gridDim.x * kThreads;
-  for (int64_t i0 = blockIdx.x * (int64_t)kThreads + threadIdx.x; i0 < total; i0 += stride * kUnroll) {
+  const Idx words_per_row = (Idx)words_per_row_arg;
+  const Idx total = (Idx)(tokens * words_per_row_arg * 2);  // 16-byte output pieces
+  const Idx stride = (Idx)gridDim.x * kThreads;
+  for (Idx i0 = blockIdx.x * (Idx)kThreads + threadIdx.x; i0 < total; i0 += stride * kUnroll) {
     uint32_t w[kUnroll];
     float s[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      const int64_t i = i0 + u * stride;
+      const Idx i = i0 + u * stride;
       if (i < total) {
-        const int64_t word = i >> 1;
+        const Idx word = i >> 1;
         w[u] = words[word] >> (16 * (int)(i & 1));  // the four nibbles of this half
-        s[u] = load_scale(scales, word / words_per_row, scale_dtype);
+        s[u] = load_scale(scales, (int64_t)(word / words_per_row), scale_dtype);
       }
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      const int64_t i = i0 + u * stride;
+      const Idx i = i0 + u * stride;
       if (i < total) {
         float4 o;
         o.x = (float)((int)(w[u] & 0xF) - 8) * s[u];
@@ -145,8 +149,11 @@ int launch_dequantize(const void* codes, const void* scales, float* out, int64_t
                       int scale_dtype, cudaStream_t stream) {
   if (packed) {
     const int64_t wpr = features / 8;
-    dequant_packed_kernel<<<grid_for((tokens * wpr * 2 + 3) / 4), kThreads, 0, stream>>>(
-        reinterpret_cast<const uint32_t*>(codes), scales, out, tokens, wpr, scale_dtype);
+    const int grid = grid_for((tokens * wpr * 2 + 3) / 4);
+    if (tokens * wpr * 2 + (int64_t)grid * kThreads * 4 < (1LL << 32))  // indices (and one step past the end) fit 32 bits
+      dequant_packed_kernel<uint32_t><<<grid, kThreads, 0, stream>>>(reinterpret_cast<const uint32_t*>(codes), scales, out, tokens, wpr, scale_dtype);
+    else
+      dequant_packed_kernel<int64_t><<<grid, kThreads, 0, stream>>>(reinterpret_cast<const uint32_t*>(codes), scales, out, tokens, wpr, scale_dtype);
     return check_launch("dequant_packed_kernel");
   }
   dequant_int8_kernel<<<grid_for(tokens * features / 16 + 1), kThreads, 0, stream>>>(
