@@ -11,38 +11,34 @@ constexpr int kThreads = 256;
 // packed: one thread per half word -> 4 floats, so that consecutive lanes write consecutive 16-byte pieces (a warp's
 // store covers 512 contiguous bytes); four items per thread are in flight.  The output is 8x the input: the kernel is
 // bound by HBM writes.
-// Idx: 32-bit indices when the piece count allows (the usual case): the row of a piece is a division, and the 64-bit one
-// costs more instructions than the rest of the loop body together.
-template <typename Idx>
+// A block works on whole rows (tokens), so the row's scale is read once and no piece needs a division to find its row.
 __global__ void __launch_bounds__(kThreads)
 dequant_packed_kernel(const uint32_t* __restrict__ words, const void* __restrict__ scales, float* __restrict__ out,
-                      int64_t tokens, int64_t words_per_row_arg, int scale_dtype) {
+                      int64_t tokens, int words_per_row, int scale_dtype) {
   constexpr int kUnroll = 4;
-  const Idx words_per_row = (Idx)words_per_row_arg;
-  const Idx total = (Idx)(tokens * words_per_row_arg * 2);  // 16-byte output pieces
-  const Idx stride = (Idx)gridDim.x * kThreads;
-  for (Idx i0 = blockIdx.x * (Idx)kThreads + threadIdx.x; i0 < total; i0 += stride * kUnroll) {
-    uint32_t w[kUnroll];
-    float s[kUnroll];
+  const int pieces = words_per_row * 2;  // 16-byte output pieces per row
+  for (int64_t row = blockIdx.x; row < tokens; row += gridDim.x) {
+    const float s = load_scale(scales, row, scale_dtype);
+    const uint32_t* wrow = words + row * words_per_row;
+    float4* orow = reinterpret_cast<float4*>(out) + row * pieces;
+    for (int p0 = threadIdx.x; p0 < pieces; p0 += kThreads * kUnroll) {
+      uint32_t w[kUnroll];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const Idx i = i0 + u * stride;
-      if (i < total) {
-        const Idx word = i >> 1;
-        w[u] = words[word] >> (16 * (int)(i & 1));  // the four nibbles of this half
-        s[u] = load_scale(scales, (int64_t)(word / words_per_row), scale_dtype);
+      for (int u = 0; u < kUnroll; ++u) {
+        const int p = p0 + u * kThreads;
+        if (p < pieces) w[u] = wrow[p >> 1] >> (16 * (p & 1));  // the four nibbles of this half word
       }
-    }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const Idx i = i0 + u * stride;
-      if (i < total) {
-        float4 o;
-        o.x = (float)((int)(w[u] & 0xF) - 8) * s[u];
-        o.y = (float)((int)((w[u] >> 4) & 0xF) - 8) * s[u];
-        o.z = (float)((int)((w[u] >> 8) & 0xF) - 8) * s[u];
-        o.w = (float)((int)((w[u] >> 12) & 0xF) - 8) * s[u];
-        __stcs(reinterpret_cast<float4*>(out) + i, o);  // streaming store: the output is not read back by this kernel
+      for (int u = 0; u < kUnroll; ++u) {
+        const int p = p0 + u * kThreads;
+        if (p < pieces) {
+          float4 o;
+          o.x = (float)((int)(w[u] & 0xF) - 8) * s;
+          o.y = (float)((int)((w[u] >> 4) & 0xF) - 8) * s;
+          o.z = (float)((int)((w[u] >> 8) & 0xF) - 8) * s;
+          o.w = (float)((int)((w[u] >> 12) & 0xF) - 8) * s;
+          __stcs(orow + p, o);  // streaming store: the output is not read back by this kernel
+        }
       }
     }
   }
@@ -149,11 +145,9 @@ int launch_dequantize(const void* codes, const void* scales, float* out, int64_t
                       int scale_dtype, cudaStream_t stream) {
   if (packed) {
     const int64_t wpr = features / 8;
-    const int grid = grid_for((tokens * wpr * 2 + 3) / 4);
-    if (tokens * wpr * 2 + (int64_t)grid * kThreads * 4 < (1LL << 32))  // indices (and one step past the end) fit 32 bits
-      dequant_packed_kernel<uint32_t><<<grid, kThreads, 0, stream>>>(reinterpret_cast<const uint32_t*>(codes), scales, out, tokens, wpr, scale_dtype);
-    else
-      dequant_packed_kernel<int64_t><<<grid, kThreads, 0, stream>>>(reinterpret_cast<const uint32_t*>(codes), scales, out, tokens, wpr, scale_dtype);
+    const int64_t cap = 148LL * 8 * 8;  // rows in flight: eight blocks per SM, a few rounds
+    dequant_packed_kernel<<<(int)(tokens < cap ? tokens : cap), kThreads, 0, stream>>>(reinterpret_cast<const uint32_t*>(codes), scales, out, tokens,
+                                                                                     (int)wpr, scale_dtype);
     return check_launch("dequant_packed_kernel");
   }
   dequant_int8_kernel<<<grid_for(tokens * features / 16 + 1), kThreads, 0, stream>>>(
