@@ -50,24 +50,22 @@ dequant_int8_kernel(const int8_t* __restrict__ codes, const void* __restrict__ s
                     int64_t tokens, int64_t features, int scale_dtype) {
   const int64_t total = tokens * features;
   if ((features & 3) == 0) {
+    // a block works on whole rows: the scale is read once per row, no group needs a division to find its row
     constexpr int kUnroll = 4;
-    const int64_t groups = total >> 2, stride = (int64_t)gridDim.x * kThreads;
-    for (int64_t g0 = blockIdx.x * (int64_t)kThreads + threadIdx.x; g0 < groups; g0 += stride * kUnroll) {
-      char4 c[kUnroll];
-      float s[kUnroll];
+    const int groups = (int)(features >> 2);  // groups of 4 codes per row
+    for (int64_t row = blockIdx.x; row < tokens; row += gridDim.x) {
+      const float s = load_scale(scales, row, scale_dtype);
+      const char4* crow = reinterpret_cast<const char4*>(codes + row * features);
+      float4* orow = reinterpret_cast<float4*>(out + row * features);
+      for (int g0 = threadIdx.x; g0 < groups; g0 += kThreads * kUnroll) {
+        char4 c[kUnroll];
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        const int64_t g = g0 + u * stride;
-        if (g < groups) {
-          c[u] = reinterpret_cast<const char4*>(codes)[g];
-          s[u] = load_scale(scales, (g << 2) / features, scale_dtype);
-        }
-      }
+        for (int u = 0; u < kUnroll; ++u)
+          if (g0 + u * kThreads < groups) c[u] = crow[g0 + u * kThreads];
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        const int64_t g = g0 + u * stride;
-        if (g < groups)
-          __stcs(reinterpret_cast<float4*>(out) + g, make_float4((float)c[u].x * s[u], (float)c[u].y * s[u], (float)c[u].z * s[u], (float)c[u].w * s[u]));
+        for (int u = 0; u < kUnroll; ++u)
+          if (g0 + u * kThreads < groups)
+            __stcs(orow + g0 + u * kThreads, make_float4((float)c[u].x * s, (float)c[u].y * s, (float)c[u].z * s, (float)c[u].w * s));
       }
     }
   } else {
