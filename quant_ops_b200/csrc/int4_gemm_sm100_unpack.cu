@@ -99,9 +99,12 @@ __device__ __forceinline__ float2 unpack_out2(uint32_t w, __nv_bfloat16) { retur
 
 // packed word -> (even elements, odd elements) as int8 bytes holding 16 * value
 __device__ __forceinline__ void split16(uint32_t w, uint32_t& even, uint32_t& odd) {
-  const uint32_t t = w ^ 0x88888888u;
-  even = (t << 4) & 0xF0F0F0F0u;
-  odd = t & 0xF0F0F0F0u;
+  // the shift as an integer multiply-add (FMA pipe), the mask and the sign flip of each operand as one three-input
+  // logic operation (ALU pipe): two ALU instructions per packed word instead of three
+  uint32_t w16;
+  asm("mad.lo.u32 %0, %1, 16, 0;" : "=r"(w16) : "r"(w));
+  asm("lop3.b32 %0, %1, 0xF0F0F0F0, 0x80808080, 0x6A;" : "=r"(even) : "r"(w16));  // (a & b) ^ c
+  asm("lop3.b32 %0, %1, 0xF0F0F0F0, 0x80808080, 0x6A;" : "=r"(odd) : "r"(w));
 }
 
 // One stage of the leader's issue loop as a single instruction sequence: probe the NEXT stage's "operands ready"
