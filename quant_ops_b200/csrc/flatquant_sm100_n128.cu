@@ -247,7 +247,9 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
         break;
       }
       tc_fence_after();
-      uint8_t* yrow = smem + kOffY + s * kStageBytes + h * y_atom + r * 128;
+      // (rows start on 128-byte boundaries: piece c of the swizzled row is at (row | (r & 7) << 4) ^ (c << 4), one logic
+      // operation per store instead of three)
+      const uint32_t yrow = (smem_base + kOffY + s * kStageBytes + h * y_atom + r * 128) | (uint32_t)((r & 7) << 4);
 #pragma unroll
       for (int p = 0; p < 2; ++p) {
         uint32_t v[32];
@@ -267,7 +269,7 @@ flatquant_n128_kernel(const __grid_constant__ CUtensorMap x_map, const T* __rest
               w.z = pack2<T>(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
               w.w = pack2<T>(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
             }
-            *reinterpret_cast<uint4*>(yrow + (((p * 4 + j) ^ (r & 7)) << 4)) = w;
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(yrow ^ (uint32_t)((p * 4 + j) << 4)), "r"(w.x), "r"(w.y), "r"(w.z), "r"(w.w) : "memory");
           }
         }
       }

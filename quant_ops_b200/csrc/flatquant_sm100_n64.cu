@@ -244,7 +244,10 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
       }
       tc_fence_after();
       const int yr = r < m ? r : r - m + k2;  // row of the Y stage: token c's rows start at c * k2
-      uint8_t* yrow = smem + kOffY + s * kStageBytes + yr * 128;
+      // (rows start on 128-byte boundaries: piece c of the swizzled row is at (row | (yr & 7) << 4) ^ (c << 4), one logic
+      // operation per store where (c ^ (yr & 7)) << 4 added to the row costs three; the Y pass shares the ALU pipe with the
+      // quantize pass)
+      const uint32_t yrow = (smem_base + kOffY + s * kStageBytes + yr * 128) | (uint32_t)((yr & 7) << 4);
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         uint32_t v[32];
@@ -262,7 +265,7 @@ flatquant_n64_kernel(const __grid_constant__ CUtensorMap x_map, const T* __restr
             w.y = pack2<T>(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
             w.z = pack2<T>(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
             w.w = pack2<T>(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
-            *reinterpret_cast<uint4*>(yrow + (((h * 4 + j) ^ (yr & 7)) << 4)) = w;
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(yrow ^ (uint32_t)((h * 4 + j) << 4)), "r"(w.x), "r"(w.y), "r"(w.z), "r"(w.w) : "memory");
           }
         }
       }
